@@ -31,6 +31,7 @@ class KVRequest:
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None        # size of a value head when it differs from the key head's
+    values_in_keys: bool = False            # the values are columns of the key rows: no value pages are kept
 
 
 @dataclass(frozen=True)
@@ -71,14 +72,15 @@ def plan_groups(requests: Mapping[int, Sequence[object]]):
                 if seen_kv:
                     raise CacheError(f"cache entry {entry} asks for keys and values twice")
                 seen_kv = True
-                kv_keys.setdefault((r.n_kv_heads, r.head_dim, r.window, r.v_head_dim or r.head_dim), []).append(entry)
+                kv_keys.setdefault((r.n_kv_heads, r.head_dim, r.window, 0 if r.values_in_keys else r.v_head_dim or r.head_dim),
+                                   []).append(entry)
             elif isinstance(r, StateRequest):
                 if r.dtype not in _TORCH:
                     raise CacheError(f"state '{r.name}': dtype {r.dtype} is not supported")
                 st_keys.setdefault((r.name, tuple(r.shape), r.dtype), []).append(entry)
             else:
                 raise CacheError(f"cache entry {entry}: unknown request {r!r}")
-    kv_groups = [KVGroupLayout(k[0], k[1], k[2], tuple(v), k[3]) for k, v in kv_keys.items()]
+    kv_groups = [KVGroupLayout(k[0], k[1], k[2], tuple(v), k[3]) for k, v in kv_keys.items()]     # v_head_dim 0: no value pages
     st_groups = [StateGroupLayout(k[1], k[2], tuple(v), k[0]) for k, v in st_keys.items()]
     return kv_groups, st_groups
 
@@ -109,7 +111,8 @@ class SequenceCache:
             for g in self.kv_groups:
                 shape = (len(g.cache_entries), n_pages, g.n_kv_heads, page_size, g.head_dim)
                 self.k.append(torch.zeros(shape, dtype=kv_dtype, device=device))
-                self.v.append(torch.zeros(shape[:-1] + (g.v_head_dim or g.head_dim,), dtype=kv_dtype, device=device))
+                self.v.append(torch.zeros(shape[:-1] + (g.head_dim if g.v_head_dim is None else g.v_head_dim,), dtype=kv_dtype,
+                                          device=device))
             for s in self.state_groups:
                 self.state.append(torch.zeros((len(s.cache_entries), max_slots) + tuple(s.shape),
                                               dtype=_TORCH[s.dtype], device=device))
@@ -121,7 +124,7 @@ class SequenceCache:
                     row = g.cache_entries.index(e)
                     view.kv_group, view.window = gi, g.window
                     if device is not None:
-                        view.k_pages, view.v_pages = self.k[gi][row], self.v[gi][row]
+                        view.k_pages, view.v_pages = self.k[gi][row], (self.v[gi][row] if g.v_head_dim != 0 else None)
             for si, s in enumerate(self.state_groups):
                 if e in s.cache_entries and device is not None:
                     view.states[s.name] = self.state[si][s.cache_entries.index(e)]
@@ -134,7 +137,8 @@ class SequenceCache:
 
     def bytes_per_token(self) -> int:
         el = torch.empty((), dtype=self.kv_dtype).element_size()
-        return sum(len(g.cache_entries) * g.n_kv_heads * (g.head_dim + (g.v_head_dim or g.head_dim)) * el for g in self.kv_groups)
+        return sum(len(g.cache_entries) * g.n_kv_heads * (g.head_dim + (g.head_dim if g.v_head_dim is None else g.v_head_dim)) * el
+                   for g in self.kv_groups)
 
     # -- slots ---------------------------------------------------------------------------------
     def alloc_slot(self) -> int:

@@ -68,7 +68,7 @@ class KVGroupLayout:
     head_dim: int
     window: Optional[int]            # None: every key is kept
     cache_entries: tuple             # cache entries (of the schedule) stored in this group, in order
-    v_head_dim: Optional[int] = None # size of a value head; None: as the key head
+    v_head_dim: Optional[int] = None # size of a value head; None: as the key head; 0: the values lie in the key rows
 
 
 @dataclass(frozen=True)

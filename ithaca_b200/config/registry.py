@@ -13,6 +13,7 @@ from typing import Any, Callable, Dict, Optional
 
 from .base import ConfigError, load_config_dict
 from .llama import LlamaConfig
+from .mimadra import MimadraConfig
 from .tiralix import TiralixConfig
 from .vebisun import VebisunConfig
 
@@ -67,3 +68,4 @@ def config_from_model_dir(model_dir: str):
 register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
 register_architecture(VebisunConfig.ARCHITECTURE, VebisunConfig)
 register_architecture(TiralixConfig.ARCHITECTURE, TiralixConfig)
+register_architecture(MimadraConfig.ARCHITECTURE, MimadraConfig)

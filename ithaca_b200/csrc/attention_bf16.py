@@ -114,10 +114,12 @@ def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_len
 
 
 def attend(q, k_pages, v_pages, ctx, table, n_heads: int, scale: float, window: int,
-           status, softcap: float = 0.0) -> Optional[torch.Tensor]:
+           status, softcap: float = 0.0, sink: bool = False) -> Optional[torch.Tensor]:
     """Returns None when no specialised kernel takes these sizes or options (the caller then uses the
     CUDA-core kernel)."""
     n_pages, nkv, page_size, hd = k_pages.shape
+    if sink:
+        return None
     if k_pages.dtype != torch.bfloat16 or q.dtype != torch.bfloat16 or page_size != 64 or not supported(hd):
         return None
     work = None

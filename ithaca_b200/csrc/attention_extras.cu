@@ -6,7 +6,8 @@
 // ------------------------------------------------------------------ norm + rotation + cache append
 // One block per token.  q = columns [q_off, q_off + nh*hd), k = [k_off, + nkv*hd), v = [v_off, + nkv*hdv).
 // With q_w / k_w: q (and k) is divided by the root mean square of ALL its nh*hd (nkv*hd) values, eps inside the root,
-// and multiplied by the weight of that size.  Then the leading `rot` dimensions of every q and k head are rotated:
+// and multiplied by the weight of that size; with per_head set, every head is divided by the root mean square of its own
+// hd values and multiplied by a weight of size hd that all heads share.  Then the leading `rot` dimensions of every q and k head are rotated:
 // pairing 0 turns (i, i + rot/2), pairing 1 turns (2i, 2i + 1), by float(pos) * inv_freq[i]; cos and sin are multiplied
 // by `magnitude`.  q goes to q_out [T, nh*hd]; k and v into the token's place in the pages
 // (pages[page][kv head][position in page][size], page = table[seq * table_stride + pos / page_size]).
@@ -17,8 +18,8 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
                         TC* __restrict__ v_pages, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                         const int* __restrict__ table, int table_stride, const float* __restrict__ inv_freq, float magnitude,
                         int nh, int nkv, int hd, int hdv, int rot, int pairing, int page_size, int n_pages, int write_cache,
-                        int* status) {
-    extern __shared__ __align__(16) float cs[];          // [rot/2] cos, [rot/2] sin
+                        int per_head, int* status) {
+    extern __shared__ __align__(16) float cs[];          // [rot/2] cos, [rot/2] sin, then per_head: [nh + nkv] 1 / rms
     __shared__ float red[32];
     ik_pdl_wait();
     IK_AFTER_WAIT(p);
@@ -34,13 +35,27 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
         cs[half + i] = sinf(ang) * magnitude;
     }
     float rq = 1.f, rk = 1.f;
-    if (q_w) {
+    float* head_r = cs + rot;
+    if (per_head) {
+        // one warp per head, lanes in index order, then the shuffle tree: the sum's order depends on hd alone
+        for (int head = threadIdx.x >> 5; head < nh + nkv; head += 8) {
+            const bool is_q = head < nh;
+            const float* src = is_q ? row + q_off + head * hd : row + k_off + (head - nh) * hd;
+            float ss = 0.f;
+            if (is_q ? q_w != nullptr : k_w != nullptr) {
+                for (int i = threadIdx.x & 31; i < hd; i += 32) { const float v = src[i]; ss = fmaf(v, v, ss); }
+                #pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            }
+            if ((threadIdx.x & 31) == 0) head_r[head] = 1.0f / sqrtf(ss / (float)hd + eps);
+        }
+    } else if (q_w) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < nh * hd; i += 256) { const float v = row[q_off + i]; ss = fmaf(v, v, ss); }
         ss = ik_block_sum<256>(ss, red);
         rq = 1.0f / sqrtf(ss / (float)(nh * hd) + eps);
     }
-    if (k_w) {
+    if (k_w && !per_head) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < nkv * hd; i += 256) { const float v = row[k_off + i]; ss = fmaf(v, v, ss); }
         ss = ik_block_sum<256>(ss, red);
@@ -61,8 +76,8 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
         const bool is_q = head < nh;
         if (!is_q && !page_ok) continue;
         const float* src = is_q ? row + q_off + head * hd : row + k_off + (head - nh) * hd;
-        const float* w = is_q ? (q_w ? q_w + head * hd : nullptr) : (k_w ? k_w + (head - nh) * hd : nullptr);
-        const float r = is_q ? rq : rk;
+        const float* w = is_q ? (q_w ? q_w + (per_head ? 0 : head * hd) : nullptr) : (k_w ? k_w + (per_head ? 0 : (head - nh) * hd) : nullptr);
+        const float r = per_head ? head_r[head] : is_q ? rq : rk;
         float val = w ? src[i] * r * w[i] : src[i];
         if (i < rot) {
             int partner, f;
@@ -89,16 +104,16 @@ IK_EXPORT int ik_norm_rope_append(const float* p, int ldp, int q_off, int k_off,
                                   float eps, void* q_out, int q_dtype, void* k_pages, void* v_pages, int cache_dtype,
                                   const int* token_seq, const int* token_pos, const int* table, int table_stride,
                                   const float* inv_freq, float magnitude, int T, int nh, int nkv, int hd, int hdv, int rot,
-                                  int pairing, int page_size, int n_pages, int write_cache, int* status, cudaStream_t stream) {
+                                  int pairing, int page_size, int n_pages, int write_cache, int per_head, int* status, cudaStream_t stream) {
     if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || hdv <= 0 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0)
         return IK_BAD_ARGUMENT;
     if (rot > 0 && !inv_freq) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
-    const size_t smem = (size_t)rot * sizeof(float);
+    const size_t smem = (size_t)(rot + (per_head ? nh + nkv : 0)) * sizeof(float);
 #define IK_NRA(TQ, TC)                                                                                                       \
     IK_RETURN_IF_ERROR(ik_launch(norm_rope_append_kernel<TQ, TC>, T, 256, smem, stream, p, ldp, q_off, k_off, v_off, q_w, k_w, eps, \
                                  (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, token_pos, table, table_stride, inv_freq,  \
-                                 magnitude, nh, nkv, hd, hdv, rot, pairing, page_size, n_pages, write_cache, status))
+                                 magnitude, nh, nkv, hd, hdv, rot, pairing, page_size, n_pages, write_cache, per_head, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_NRA(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_NRA(__nv_bfloat16, __nv_bfloat16);
     else return IK_BAD_ARGUMENT;
@@ -106,11 +121,12 @@ IK_EXPORT int ik_norm_rope_append(const float* p, int ldp, int q_off, int k_off,
     IK_LAUNCH_STATUS();
 }
 
-// ------------------------------------------------------------------ a gate per head
+// ------------------------------------------------------------------ a gate per head, or per value
 // out[t, h * hdv + j] = att[t, h * hdv + j] * sigmoid(p[t, g_off + h]) * mult (no gate without p); out has row stride ldo.
+// wide: the gate has one number per value, p[t, g_off + h * hdv + j].
 template <typename TA>
 __global__ void head_gate_kernel(const TA* __restrict__ att, const float* __restrict__ p, int ldp, int g_off, TA* __restrict__ out,
-                                 int ldo, int H, int hdv, size_t total, float mult) {
+                                 int ldo, int H, int hdv, size_t total, float mult, int wide) {
     ik_pdl_wait();
     IK_AFTER_WAIT(att);
     IK_AFTER_WAIT(p);
@@ -120,7 +136,7 @@ __global__ void head_gate_kernel(const TA* __restrict__ att, const float* __rest
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const size_t t = idx / cols;
         const int c = (int)(idx - t * cols), h = c / hdv;
-        const float g = p ? 1.0f / (1.0f + expf(-p[t * ldp + g_off + h])) : 1.0f;
+        const float g = p ? 1.0f / (1.0f + expf(-p[t * ldp + g_off + (wide ? c : h)])) : 1.0f;
         ik_st(out, t * ldo + c, ik_ld(att, idx) * g * mult);
     }
 }
@@ -128,7 +144,7 @@ __global__ void head_gate_kernel(const TA* __restrict__ att, const float* __rest
 // The same by fours (head sizes and row distances that are multiples of four, aligned pointers): one sigmoid per four values.
 template <typename TA>
 __global__ void head_gate4_kernel(const TA* __restrict__ att, const float* __restrict__ p, int ldp, int g_off, TA* __restrict__ out,
-                                  int ldo, int H, int hdv, size_t total4, float mult) {
+                                  int ldo, int H, int hdv, size_t total4, float mult, int wide) {
     ik_pdl_wait();
     IK_AFTER_WAIT(att);
     IK_AFTER_WAIT(p);
@@ -138,15 +154,21 @@ __global__ void head_gate4_kernel(const TA* __restrict__ att, const float* __res
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total4; idx += stride) {
         const size_t t = idx / cols4;
         const int c = (int)(idx - t * cols4) * 4, h = c / hdv;
-        const float g = (p ? 1.0f / (1.0f + expf(-p[t * ldp + g_off + h])) : 1.0f);
         float4 v = ik_ld4(att, t * (size_t)(H * hdv) + c);
-        v.x = v.x * g * mult; v.y = v.y * g * mult; v.z = v.z * g * mult; v.w = v.w * g * mult;
+        if (wide && p) {
+            const float* gp = p + t * ldp + g_off + c;
+            v.x = v.x * (1.0f / (1.0f + expf(-gp[0]))) * mult; v.y = v.y * (1.0f / (1.0f + expf(-gp[1]))) * mult;
+            v.z = v.z * (1.0f / (1.0f + expf(-gp[2]))) * mult; v.w = v.w * (1.0f / (1.0f + expf(-gp[3]))) * mult;
+        } else {
+            const float g = (p ? 1.0f / (1.0f + expf(-p[t * ldp + g_off + h])) : 1.0f);
+            v.x = v.x * g * mult; v.y = v.y * g * mult; v.z = v.z * g * mult; v.w = v.w * g * mult;
+        }
         ik_st4(out, t * ldo + c, v);
     }
 }
 
 IK_EXPORT int ik_head_gate(const void* att, const float* p, int ldp, int g_off, void* out, int dtype, int ldo, int T, int H,
-                           int hdv, float mult, cudaStream_t stream) {
+                           int hdv, float mult, int wide, cudaStream_t stream) {
     if (T < 0 || H <= 0 || hdv <= 0 || ldo < H * hdv) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const size_t total = (size_t)T * H * hdv;
@@ -154,18 +176,18 @@ IK_EXPORT int ik_head_gate(const void* att, const float* p, int ldp, int g_off, 
         const size_t total4 = total / 4;
         const int blocks4 = (int)((total4 + 255) / 256 < 65535 * 16 ? (total4 + 255) / 256 : 65535 * 16);
         if (dtype == IK_F32)
-            IK_RETURN_IF_ERROR(ik_launch(head_gate4_kernel<float>, blocks4, 256, 0, stream, (const float*)att, p, ldp, g_off, (float*)out, ldo, H, hdv, total4, mult));
+            IK_RETURN_IF_ERROR(ik_launch(head_gate4_kernel<float>, blocks4, 256, 0, stream, (const float*)att, p, ldp, g_off, (float*)out, ldo, H, hdv, total4, mult, wide));
         else
             IK_RETURN_IF_ERROR(ik_launch(head_gate4_kernel<__nv_bfloat16>, blocks4, 256, 0, stream, (const __nv_bfloat16*)att, p, ldp, g_off,
-                                         (__nv_bfloat16*)out, ldo, H, hdv, total4, mult));
+                                         (__nv_bfloat16*)out, ldo, H, hdv, total4, mult, wide));
         IK_LAUNCH_STATUS();
     }
     const int blocks = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
     if (dtype == IK_F32)
-        IK_RETURN_IF_ERROR(ik_launch(head_gate_kernel<float>, blocks, 256, 0, stream, (const float*)att, p, ldp, g_off, (float*)out, ldo, H, hdv, total, mult));
+        IK_RETURN_IF_ERROR(ik_launch(head_gate_kernel<float>, blocks, 256, 0, stream, (const float*)att, p, ldp, g_off, (float*)out, ldo, H, hdv, total, mult, wide));
     else if (dtype == IK_BF16)
         IK_RETURN_IF_ERROR(ik_launch(head_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)att, p, ldp, g_off,
-                                     (__nv_bfloat16*)out, ldo, H, hdv, total, mult));
+                                     (__nv_bfloat16*)out, ldo, H, hdv, total, mult, wide));
     else return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();
 }

@@ -7,7 +7,9 @@
 // Scores, the running maximum, the sum and the output are float; exp is the accurate
 // function.  This is the 32-bit path's attention and the fallback for head sizes the
 // tensor-core kernels do not take.  Options: a cap on the scores, s <- cap * tanh(s / cap) after the scale
-// (cap 0 = none), and value heads of another size than the key heads (hdv).
+// (cap 0 = none), value heads of another size than the key heads (hdv), values that are the leading hdv columns of the
+// key rows themselves (v_pages = k_pages with ldv = hd: a latent that serves as key and value), and a sink: one more
+// key of score 0 that carries no value, so that the weights are exp(s_j) / (1 + sum exp(s_j)).
 #include <math.h>
 #define IK_FAMILY 4
 #include "common.cuh"
@@ -21,8 +23,8 @@ template <typename TQ, typename TC, typename TO>
 __global__ void __launch_bounds__(TILE)
 attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, const TC* __restrict__ v_pages,
                       TO* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
-                      const int* __restrict__ table, int table_stride, int nh, int nkv, int hd, int hdv, float scale,
-                      float softcap, int window, int page_size, int n_pages, int* status) {
+                      const int* __restrict__ table, int table_stride, int nh, int nkv, int hd, int hdv, int ldv, float scale,
+                      float softcap, int window, int sink, int page_size, int n_pages, int* status) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem[];
@@ -39,7 +41,8 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
     const TQ* qrow = q + ((size_t)t * nh + h) * hd;
     for (int i = tid; i < hd; i += TILE) qs[i] = ik_ld(qrow, i);
 
-    float m = -INFINITY, l = 0.f, o[MAX_R];
+    // the sink stands at the head of the running softmax: a maximum of 0 whose weight exp(0 - 0) = 1 is already in the sum
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f, o[MAX_R];
     #pragma unroll
     for (int r = 0; r < MAX_R; r++) o[r] = 0.f;
     __syncthreads();
@@ -79,7 +82,7 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
                 float acc = o[r] * alpha;
                 for (int jj = 0; jj < n_in_tile; jj++) {
                     const float pj = sc[jj];
-                    if (pj != 0.f) acc = fmaf(pj, ik_ld(v_pages + row[jj] * hdv, i), acc);
+                    if (pj != 0.f) acc = fmaf(pj, ik_ld(v_pages + row[jj] * ldv, i), acc);
                 }
                 o[r] = acc;
             }
@@ -100,8 +103,9 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
 
 IK_EXPORT int ik_attention_simt(const void* q, int q_dtype, const void* k_pages, const void* v_pages, int cache_dtype,
                                 void* out, int out_dtype, const int* token_seq, const int* token_pos, const int* table,
-                                int table_stride, int T, int nh, int nkv, int hd, int hdv, float scale, float softcap, int window,
-                                int page_size, int n_pages, int* status, cudaStream_t stream) {
+                                int table_stride, int T, int nh, int nkv, int hd, int hdv, int ldv, float scale, float softcap, int window,
+                                int sink, int page_size, int n_pages, int* status, cudaStream_t stream) {
+    if (ldv < hdv) return IK_BAD_ARGUMENT;
     if (T < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hdv <= 0 || hdv > TILE * MAX_R || page_size <= 0 || softcap < 0.f) return IK_BAD_ARGUMENT;
     if (q_dtype != out_dtype) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
@@ -109,7 +113,7 @@ IK_EXPORT int ik_attention_simt(const void* q, int q_dtype, const void* k_pages,
     const size_t smem = (size_t)(hd + TILE + 32) * sizeof(float) + TILE * sizeof(size_t);
 #define IK_ATT(TQ, TC)                                                                                                \
     IK_RETURN_IF_ERROR(ik_launch(attention_simt_kernel<TQ, TC, TQ>, grid, TILE, smem, stream, (const TQ*)q, (const TC*)k_pages, (const TC*)v_pages, \
-        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, hdv, scale, softcap, window, page_size, n_pages, status))
+        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, hdv, ldv, scale, softcap, window, sink, page_size, n_pages, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_ATT(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_ATT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_ATT(float, __nv_bfloat16);

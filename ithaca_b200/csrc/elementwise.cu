@@ -171,6 +171,91 @@ IK_EXPORT int ik_rmsnorm_add(const float* y, const float* w, const float* scale,
     IK_LAUNCH_STATUS();
 }
 
+// ------------------------------------------------------------------ sublayer result into the stream, then the next norm
+// residual += scale * y (scale: a vector, "layer scale"; absent = ones), one block per row.  With w, the new row's RMS norm
+// times w goes to `normed` in its own type: the add that closes one sublayer and the norm that opens the next in one pass
+// over the row.  The row of up to 8192 values stays in registers between the two.
+constexpr int SAN_PER = 32;
+template <typename TO>
+__global__ void __launch_bounds__(256)
+scale_add_norm_kernel(const float* __restrict__ y, const float* __restrict__ scale, float* __restrict__ residual,
+                      const float* __restrict__ w, TO* __restrict__ normed, int d, float eps) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(y);
+    IK_AFTER_WAIT(residual);
+    ik_pdl_launch_dependents();
+    __shared__ float red[32];
+    const float* a = y + (size_t)blockIdx.x * d;
+    float* res = residual + (size_t)blockIdx.x * d;
+    const bool in_regs = d <= 256 * SAN_PER;
+    float keep[SAN_PER];
+    float ss = 0.f;
+    #pragma unroll
+    for (int j = 0; j < SAN_PER; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < d) {
+            const float r = fmaf(scale ? scale[i] : 1.0f, a[i], res[i]);
+            res[i] = r;
+            keep[j] = r;
+            ss = fmaf(r, r, ss);
+        }
+    }
+    for (int i = threadIdx.x + 256 * SAN_PER; i < d; i += 256) {
+        const float r = fmaf(scale ? scale[i] : 1.0f, a[i], res[i]);
+        res[i] = r;
+        ss = fmaf(r, r, ss);
+    }
+    if (!w) return;
+    ss = ik_block_sum<256>(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = normed + (size_t)blockIdx.x * d;
+    #pragma unroll
+    for (int j = 0; j < SAN_PER; j++) {
+        const int i = threadIdx.x + j * 256;
+        if (i < d) ik_st(o, i, keep[j] * s * w[i]);
+    }
+    if (!in_regs)
+        for (int i = threadIdx.x + 256 * SAN_PER; i < d; i += 256) ik_st(o, i, res[i] * s * w[i]);
+}
+
+IK_EXPORT int ik_scale_add_norm(const float* y, const float* scale, float* residual, const float* w, void* normed, int out_dtype,
+                                int rows, int d, float eps, cudaStream_t stream) {
+    if (rows < 0 || d <= 0 || !y || !residual || (w && !normed)) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    if (w && out_dtype == IK_BF16)
+        IK_RETURN_IF_ERROR(ik_launch(scale_add_norm_kernel<__nv_bfloat16>, rows, 256, 0, stream, y, scale, residual, w, (__nv_bfloat16*)normed, d, eps));
+    else if (!w || out_dtype == IK_F32)
+        IK_RETURN_IF_ERROR(ik_launch(scale_add_norm_kernel<float>, rows, 256, 0, stream, y, scale, residual, w, (float*)normed, d, eps));
+    else
+        return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
+// ------------------------------------------------------------------ activation of an ungated feed-forward
+// kind 0: relu(x)^2;  kind 1: gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).
+__device__ __forceinline__ float ik_plain_act_value(float x, int kind) {
+    if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+template <typename TO>
+__global__ void plain_act_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t total, int kind) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(x);
+    ik_pdl_launch_dependents();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) ik_st(out, i, ik_plain_act_value(x[i], kind));
+}
+
+IK_EXPORT int ik_plain_act(const float* x, void* out, int out_dtype, unsigned long long total, int kind, cudaStream_t stream) {
+    if (kind < 0 || kind > 1) return IK_BAD_ARGUMENT;
+    if (total == 0) return IK_OK;
+    const int blocks = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+    if (out_dtype == IK_F32) IK_RETURN_IF_ERROR(ik_launch(plain_act_kernel<float>, blocks, 256, 0, stream, x, (float*)out, (size_t)total, kind));
+    else if (out_dtype == IK_BF16) IK_RETURN_IF_ERROR(ik_launch(plain_act_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, (__nv_bfloat16*)out, (size_t)total, kind));
+    else return IK_BAD_ARGUMENT;
+    IK_LAUNCH_STATUS();
+}
+
 // ------------------------------------------------------------------ cast
 // out[r, c] = in[r * ld_in + c] for c < cols, float to the output's type (a column range of a wider float matrix as the
 // next product's operand).

@@ -4,7 +4,8 @@
 // refuse.  Operands are converted to float when loaded; every output element is one
 // float accumulator that adds its K products in ascending k, whatever M and N are, so a
 // row of Y does not depend on which other rows are in the call.  No split along K, no
-// atomics, no reduced-precision matrix mode.
+// atomics, no reduced-precision matrix mode.  A batch of products of equal shape (one per head, say) runs as one
+// launch: product b reads X + b * bx, W + b * bw and writes Y + b * by.
 #define IK_FAMILY 2
 #include "common.cuh"
 
@@ -15,7 +16,10 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restrict__ Y, int M, int N, int K,
-                 int ldx, int ldw, int ldy, int accumulate) {
+                 int ldx, int ldw, int ldy, int accumulate, size_t bx, size_t bw, size_t by) {
+    X += blockIdx.z * bx;
+    W += blockIdx.z * bw;
+    Y += blockIdx.z * by;
     ik_pdl_wait();
     IK_AFTER_WAIT(X);                 // the tokens are the kernel before's results; this kernel takes no weight early
     ik_pdl_launch_dependents();
@@ -72,10 +76,10 @@ gemm_simt_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restr
 
 template <typename TX, typename TW, typename TY>
 int launch(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy, int accumulate,
-           cudaStream_t stream) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+           cudaStream_t stream, int batch = 1, size_t bx = 0, size_t bw = 0, size_t by = 0) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     IK_RETURN_IF_ERROR(ik_launch(gemm_simt_kernel<TX, TW, TY>, grid, 256, 0, stream, (const TX*)X, (const TW*)W, (TY*)Y, M, N, K, ldx, ldw, ldy,
-                                                            accumulate));
+                                                            accumulate, bx, bw, by));
     IK_LAUNCH_STATUS();
 }
 
@@ -97,6 +101,24 @@ IK_EXPORT int ik_gemm_simt(const void* X, int x_dtype, const void* W, int w_dtyp
         case 5: return launch<__nv_bfloat16, float, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
         case 6: return launch<__nv_bfloat16, __nv_bfloat16, float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
         case 7: return launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+    }
+    return IK_BAD_ARGUMENT;
+}
+
+// `batch` products of one shape in one launch (strides between them in elements).  x and y have one type (the activations'),
+// w its own.
+IK_EXPORT int ik_gemm_simt_batched(const void* X, int x_dtype, const void* W, int w_dtype, void* Y, int y_dtype, int M, int N,
+                                   int K, int ldx, int ldw, int ldy, int batch, unsigned long long bx, unsigned long long bw,
+                                   unsigned long long by, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || ldy < N || batch <= 0 || batch > 65535) return IK_BAD_ARGUMENT;
+    if (M == 0) return IK_OK;
+    const int code = x_dtype * 4 + w_dtype * 2 + y_dtype;
+    switch (code) {
+        case 0: return launch<float, float, float>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream, batch, bx, bw, by);
+        case 2: return launch<float, __nv_bfloat16, float>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream, batch, bx, bw, by);
+        case 4: return launch<__nv_bfloat16, float, float>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream, batch, bx, bw, by);
+        case 6: return launch<__nv_bfloat16, __nv_bfloat16, float>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream, batch, bx, bw, by);
+        case 7: return launch<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream, batch, bx, bw, by);
     }
     return IK_BAD_ARGUMENT;
 }

@@ -84,7 +84,15 @@ _SIGNATURES = {
     "ik_rope_table": [_vp, _vp, _vp, _i, _i, _vp],
     "ik_gemm_qkv_rope_mma": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_qkv_rope_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
-    "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp, _vp],
+    "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _vp, _vp],
+    "ik_gemm_simt_batched": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _u64, _u64, _u64, _vp],
+    "ik_scale_add_norm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+    "ik_plain_act": [_vp, _vp, _i, _u64, _i, _vp],
+    "ik_delta_prepare": [_vp, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp],
+    "ik_delta_rule": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_head_norm_gate": [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "ik_latent_prepare": [_vp, _i, _i, _i, _vp, _f, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
+                          _vp, _vp],
     "ik_layernorm": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _f, _vp],
     "ik_add": [_vp, _vp, _u64, _vp],
     "ik_conv_rope_append": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i,
@@ -112,8 +120,8 @@ _SIGNATURES = {
     "ik_selective_scan": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "ik_decay_attention": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_norm_rope_append": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _i, _i,
-                            _i, _i, _i, _i, _i, _i, _vp, _vp],
-    "ik_head_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _f, _vp],
+                            _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    "ik_head_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ik_gated_rmsnorm": [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _vp],
 }
 
@@ -578,16 +586,24 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages
 
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,
                    token_pos: torch.Tensor, table: torch.Tensor, n_heads: int, scale: float, window: int,
-                   status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
+                   status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, softcap: float = 0.0, sink: bool = False,
+                   values_in_keys: int = 0) -> torch.Tensor:
     """``softcap``: scores become cap * tanh(score / cap) after the scale (0 = no cap).  The value pages may
-    have a head size of their own; the output is then [T, n_heads * that size]."""
+    have a head size of their own; the output is then [T, n_heads * that size].  ``sink``: one more key of score 0
+    that carries no value (the weights are exp(s_j) / (1 + sum exp(s_j))).  ``values_in_keys`` = n > 0: a key row's
+    leading n columns are its value (``v_pages`` is not read)."""
     _need(q, "q")
     _need(k_pages, "k_pages")
-    _need(v_pages, "v_pages")
     _need(table, "table", torch.int32)
     n_pages, nkv, page_size, hd = k_pages.shape
-    hdv = v_pages.shape[3]
     T = q.shape[0]
+    if values_in_keys:
+        if not 0 < values_in_keys <= hd:
+            raise KernelError("attention: the values cannot be wider than the key rows they lie in")
+        v_pages, hdv, ldv = k_pages, int(values_in_keys), hd
+    else:
+        _need(v_pages, "v_pages")
+        hdv = ldv = v_pages.shape[3]
     if q.shape[1] != n_heads * hd or v_pages.shape[:3] != k_pages.shape[:3] or v_pages.dtype != k_pages.dtype:
         raise KernelError("attention: q or the value pages have the wrong shape")
     if out is None:
@@ -595,7 +611,8 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
     _work(f"attention_simt {T}x{n_heads}", _nbytes(q, out))
     _check(lib().ik_attention_simt(_ptr(q), _code(q), _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(out),
                                    _code(out), _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), T,
-                                   n_heads, nkv, hd, hdv, scale, softcap, window, page_size, n_pages, _ptr(status), _stream()),
+                                   n_heads, nkv, hd, hdv, ldv, scale, softcap, window, 1 if sink else 0, page_size, n_pages,
+                                   _ptr(status), _stream()),
            "attention_simt")
     return out
 
@@ -1060,8 +1077,10 @@ def decay_attention(p: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: 
 def norm_rope_append(p: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
                      eps: float, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,
                      token_pos: torch.Tensor, table: torch.Tensor, inv_freq: Optional[torch.Tensor], magnitude: float,
-                     n_heads: int, rotary_dim: int, pairing: int, write_cache: bool, status: Optional[torch.Tensor]) -> None:
-    """RMS norm of q and of k over their whole projections (``q_w``, ``k_w``: weights of that size; None = no norm),
+                     n_heads: int, rotary_dim: int, pairing: int, write_cache: bool, status: Optional[torch.Tensor],
+                     per_head: bool = False) -> None:
+    """RMS norm of q and of k over their whole projections (``q_w``, ``k_w``: weights of that size; None = no norm;
+    ``per_head``: every head over its own values, with a weight of one head's size that the heads share),
     rotation of each head's leading ``rotary_dim`` dimensions with cos and sin times ``magnitude``, q to ``q_out``,
     k and v into the pages.  q, k, v are column ranges of ``p`` (float)."""
     _need(p, "p", torch.float32, contiguous=False)
@@ -1074,32 +1093,34 @@ def norm_rope_append(p: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w: O
     T = p.shape[0]
     if p.stride(1) != 1 or q_out.shape != (T, n_heads * hd) or v_pages.shape[:3] != k_pages.shape[:3] or v_pages.dtype != k_pages.dtype \
             or max(q_off + n_heads * hd, k_off + nkv * hd, v_off + nkv * hdv) > p.shape[1] \
-            or (q_w is not None and q_w.numel() != n_heads * hd) or (k_w is not None and k_w.numel() != nkv * hd):
+            or (q_w is not None and q_w.numel() != (hd if per_head else n_heads * hd)) \
+            or (k_w is not None and k_w.numel() != (hd if per_head else nkv * hd)):
         raise KernelError("norm_rope_append: the sizes do not fit together")
     _work(f"norm_rope_append {T}", T * ((n_heads + nkv) * hd + nkv * hdv) * 4 + _nbytes(q_out) + T * nkv * (hd + hdv) * k_pages.element_size())
     _check(lib().ik_norm_rope_append(_ptr(p), p.stride(0), q_off, k_off, v_off, _ptr(q_w), _ptr(k_w), eps, _ptr(q_out), _code(q_out),
                                      _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(token_seq), _ptr(token_pos), _ptr(table),
                                      table.stride(0), _ptr(inv_freq), magnitude, T, n_heads, nkv, hd, hdv, rotary_dim, pairing,
-                                     page_size, n_pages, 1 if write_cache else 0, _ptr(status), _stream()), "norm_rope_append")
+                                     page_size, n_pages, 1 if write_cache else 0, 1 if per_head else 0, _ptr(status), _stream()), "norm_rope_append")
 
 
-def head_gate(att: torch.Tensor, p: Optional[torch.Tensor], g_off: int, out: torch.Tensor, n_heads: int, mult: float = 1.0) -> torch.Tensor:
+def head_gate(att: torch.Tensor, p: Optional[torch.Tensor], g_off: int, out: torch.Tensor, n_heads: int, mult: float = 1.0,
+              wide: bool = False) -> torch.Tensor:
     """out[t, h, :] = att[t, h, :] * sigmoid(p[t, g_off + h]) * mult (``p`` None: no gate); ``out`` may be a column range of
-    a wider matrix."""
+    a wider matrix.  ``wide``: the gate has one number per value, p[t, g_off + column]."""
     _need(att, "att")
     _need(out, "out", att.dtype, contiguous=False)
     T, cols = att.shape
     ldp = 0
     if p is not None:
         _need(p, "p", torch.float32, contiguous=False)
-        if p.stride(1) != 1 or g_off + n_heads > p.shape[1]:
+        if p.stride(1) != 1 or g_off + (cols if wide else n_heads) > p.shape[1]:
             raise KernelError("head_gate: the gate has the wrong shape")
         ldp = p.stride(0)
     if cols % n_heads or out.shape != att.shape or out.stride(1) != 1:
         raise KernelError("head_gate: the sizes do not fit together")
     _work(f"head_gate {T}x{cols}", 2 * _nbytes(att))
     _check(lib().ik_head_gate(_ptr(att), _ptr(p), ldp, g_off, _ptr(out), _code(att), out.stride(0), T, n_heads,
-                              cols // n_heads, mult, _stream()), "head_gate")
+                              cols // n_heads, mult, 1 if wide else 0, _stream()), "head_gate")
     return out
 
 
@@ -1123,3 +1144,151 @@ def gated_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, p: Optional
     _check(lib().ik_gated_rmsnorm(_ptr(x), _ptr(weight), _ptr(p), ldp, g_off, _ptr(out), _code(out), out.stride(0), rows, d, eps,
                                   mult, _stream()), "gated_rmsnorm")
     return out
+
+
+# ---------------------------------------------------------------------------------------------
+# A layer-scaled sublayer result into the stream (with the next norm), the ungated feed-forward's activation
+def scale_add_norm(y: torch.Tensor, scale: Optional[torch.Tensor], residual: torch.Tensor, weight: Optional[torch.Tensor] = None,
+                   eps: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """residual += scale * y (``scale``: a vector or None).  With ``weight``: returns rmsnorm(new residual) * weight in
+    ``out_dtype``, formed in the same pass over the rows."""
+    _need(y, "y", torch.float32)
+    _need(residual, "residual", torch.float32)
+    d = y.shape[-1]
+    if residual.shape != y.shape or (scale is not None and scale.numel() != d) or (weight is not None and weight.numel() != d):
+        raise KernelError("scale_add_norm: the sizes do not fit together")
+    if scale is not None:
+        _need(scale, "scale", torch.float32)
+    rows = y.numel() // d
+    out = None
+    if weight is not None:
+        _need(weight, "weight", torch.float32)
+        out = torch.empty((rows, d), dtype=out_dtype or torch.float32, device=y.device)
+    _work(f"scale_add{' +rmsnorm' if weight is not None else ''} {rows}x{d}", rows * d * 12 + _nbytes(out))
+    _check(lib().ik_scale_add_norm(_ptr(y), _ptr(scale), _ptr(residual), _ptr(weight), _ptr(out), _code(out) if out is not None else F32,
+                                   rows, d, eps, _stream()), "scale_add_norm")
+    return out
+
+
+PLAIN_ACTS = {"relu2": 0, "gelu_tanh": 1}
+
+
+def plain_act(x: torch.Tensor, out_dtype: torch.dtype, act: str) -> torch.Tensor:
+    """relu(x)^2 (``relu2``) or the tanh form of gelu (``gelu_tanh``), float in, ``out_dtype`` out."""
+    _need(x, "x", torch.float32)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _work(f"plain_act {x.numel()}", _nbytes(x, out))
+    _check(lib().ik_plain_act(_ptr(x), _ptr(out), _code(out), x.numel(), PLAIN_ACTS[act], _stream()), "plain_act")
+    return out
+
+
+def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One product per head in one launch: out[:, h, :] = x[:, h, :] @ w[h]^T.  ``x`` [T, H, K] and ``out`` [T, H, N] may be
+    column ranges of wider rows (their last dimension contiguous), ``w`` [H, N, K]; float accumulation in ascending k."""
+    _need(x, "x", contiguous=False)
+    _need(w, "w")
+    _need(out, "out", contiguous=False)
+    T, H, K = x.shape
+    if w.shape[0] != H or w.shape[2] != K or out.shape != (T, H, w.shape[1]) or x.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError("gemm_heads: the sizes do not fit together")
+    N = w.shape[1]
+    _work(f"gemm_heads {H}x{T}x{N}x{K}", _nbytes(w) + T * H * (K * x.element_size() + N * out.element_size()), 2 * T * H * N * K)
+    _check(lib().ik_gemm_simt_batched(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), T, N, K, x.stride(0), K, out.stride(0),
+                                      H, x.stride(1), N * K, out.stride(1), _stream()), "gemm_heads")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# The gated delta rule
+def delta_prepare(u: torch.Tensor, q_off: int, k_off: int, p: torch.Tensor, b_off: int, a_off: int, A_log: torch.Tensor,
+                  dt_bias: torch.Tensor, n_qk_heads: int, dk: int, n_heads: int, q_mult: float, unit_eps: float) -> torch.Tensor:
+    """In place: every q and k head of ``u`` (float, behind convolution and activation) becomes a unit vector, q times
+    ``q_mult``.  Returns float [T, 2, heads]: the steps sigmoid(p_b) and the decays exp(-exp(A_log) softplus(p_a + dt_bias))."""
+    _need(u, "u", torch.float32)
+    _need(p, "p", torch.float32, contiguous=False)
+    _need(A_log, "A_log", torch.float32)
+    _need(dt_bias, "dt_bias", torch.float32)
+    T = u.shape[0]
+    if p.stride(1) != 1 or max(b_off, a_off) + n_heads > p.shape[1] or max(q_off, k_off) + n_qk_heads * dk > u.shape[1] \
+            or A_log.numel() != n_heads or dt_bias.numel() != n_heads:
+        raise KernelError("delta_prepare: the sizes do not fit together")
+    bg = torch.empty((T, 2, n_heads), dtype=torch.float32, device=u.device)
+    _work(f"delta_prepare {T}", 2 * T * 2 * n_qk_heads * dk * 4)
+    _check(lib().ik_delta_prepare(_ptr(u), u.stride(0), q_off, k_off, _ptr(p), p.stride(0), b_off, a_off, _ptr(A_log), _ptr(dt_bias),
+                                  _ptr(bg), T, n_qk_heads, dk, n_heads, q_mult, unit_eps, _stream()), "delta_prepare")
+    return bg
+
+
+def delta_rule(u: torch.Tensor, q_off: int, k_off: int, v_off: int, bg: torch.Tensor, state: torch.Tensor, ctx, n_heads: int,
+               n_qk_heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The gated delta rule over the step's tokens: per head S <- g S; u = b (v - S^T k); S <- S + k u^T; o = S^T q.  q, k
+    (``n_qk_heads`` heads, unit vectors) and v are column ranges of ``u`` (float), ``bg`` [T, 2, heads] the steps and decays,
+    ``state`` [max_slots, 2, heads, dk, dv] float.  Returns float [T, heads * dv]."""
+    _need(u, "u", torch.float32)
+    _need(bg, "bg", torch.float32)
+    _need(state, "state", torch.float32)
+    T = u.shape[0]
+    if tuple(state.shape[1:]) != (2, n_heads, dk, dv) or bg.shape != (T, 2, n_heads) or n_heads % n_qk_heads \
+            or max(q_off + n_qk_heads * dk, k_off + n_qk_heads * dk, v_off + n_heads * dv) > u.shape[1]:
+        raise KernelError("delta_rule: the sizes do not fit together")
+    out = torch.empty((T, n_heads * dv), dtype=torch.float32, device=u.device)
+    _work(f"delta_rule {T}x{n_heads}x{dk}x{dv}", T * (2 * n_qk_heads * dk + 2 * n_heads * dv) * 4 + 8 * ctx.n_seqs * n_heads * dk * dv,
+          6 * T * n_heads * dk * dv)
+    _check(lib().ik_delta_rule(_ptr(u), u.stride(0), q_off, k_off, v_off, _ptr(bg), _ptr(state), _ptr(ctx.slots), _ptr(ctx.cu_seqlens),
+                               _ptr(ctx.kv_lens), _ptr(out), T, ctx.n_seqs, n_heads, n_qk_heads, dk, dv, 1 if ctx.is_decode else 0,
+                               _stream()), "delta_rule")
+    return out
+
+
+HEAD_GATES = {None: 0, "silu": 1, "sigmoid": 2}
+
+
+def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, p: Optional[torch.Tensor], g_off: int, n_heads: int,
+                   out_dtype: torch.dtype, gate: Optional[str] = "silu") -> torch.Tensor:
+    """RMS norm of every head of ``x`` [T, heads * dv] over its dv values with one weight of size dv, times
+    silu or sigmoid of columns ``g_off``.. of ``p`` (``gate`` None: no gate)."""
+    _need(x, "x", torch.float32)
+    _need(weight, "weight", torch.float32)
+    T, cols = x.shape
+    dv = cols // n_heads
+    ldp = 0
+    if gate is not None:
+        _need(p, "p", torch.float32, contiguous=False)
+        if p.stride(1) != 1 or g_off + cols > p.shape[1]:
+            raise KernelError("head_norm_gate: the gate has the wrong shape")
+        ldp = p.stride(0)
+    if cols % n_heads or weight.numel() != dv:
+        raise KernelError("head_norm_gate: the sizes do not fit together")
+    out = torch.empty((T, cols), dtype=out_dtype, device=x.device)
+    _work(f"head_norm_gate {T}x{cols}", T * cols * (8 + out.element_size()))
+    _check(lib().ik_head_norm_gate(_ptr(x), _ptr(weight), _ptr(p) if gate is not None else 0, ldp, g_off, _ptr(out), _code(out), T,
+                                   n_heads, dv, eps, HEAD_GATES[gate], _stream()), "head_norm_gate")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Latent attention
+def latent_prepare(p: torch.Tensor, q_off: int, c_off: int, c_w: Optional[torch.Tensor], eps: float, q_plain: torch.Tensor,
+                   q_full: torch.Tensor, k_pages: torch.Tensor, token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
+                   inv_freq: torch.Tensor, n_heads: int, dk: int, dr: int, rank: int, write_cache: bool,
+                   status: Optional[torch.Tensor]) -> None:
+    """From the projections ``p`` (float): every query head's plain part to ``q_plain`` [T, heads, dk], its turning part,
+    turned, to the last ``dr`` columns of ``q_full`` [T, heads, rank + dr]; when the layer writes rows, the normed latent
+    and the turned shared key part into the token's row of ``k_pages`` [pages, 1, page_size, rank + dr]."""
+    _need(p, "p", torch.float32, contiguous=False)
+    _need(q_plain, "q_plain")
+    _need(q_full, "q_full", q_plain.dtype)
+    _need(k_pages, "k_pages")
+    _need(table, "table", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    n_pages, nkv, page_size, hd = k_pages.shape
+    T = p.shape[0]
+    if p.stride(1) != 1 or nkv != 1 or hd != rank + dr or q_plain.shape != (T, n_heads * dk) or q_full.shape != (T, n_heads * hd) \
+            or inv_freq.numel() != dr // 2 or q_off + n_heads * (dk + dr) > p.shape[1] \
+            or (write_cache and (c_w is None or c_w.numel() != rank or c_off + hd > p.shape[1])):
+        raise KernelError("latent_prepare: the sizes do not fit together")
+    _work(f"latent_prepare {T}", T * (n_heads * (dk + dr) * (4 + q_plain.element_size()) + hd * (4 + k_pages.element_size())))
+    _check(lib().ik_latent_prepare(_ptr(p), p.stride(0), q_off, c_off, _ptr(c_w), eps, _ptr(q_plain), _ptr(q_full), _code(q_plain),
+                                   _ptr(k_pages), _code(k_pages), _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0),
+                                   _ptr(inv_freq), T, n_heads, dk, dr, rank, page_size, n_pages, 1 if write_cache else 0,
+                                   _ptr(status), _stream()), "latent_prepare")

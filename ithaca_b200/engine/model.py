@@ -8,11 +8,12 @@ does for the last row (src/model.cpp:1588-1594).
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, List, Mapping, Optional
 
 import torch
 
-from ..cache.cache import SequenceCache
+from ..cache.cache import KVRequest, SequenceCache
 from ..config import ConfigError, config_from_model_dir
 from ..config.spec import ModelSpec, validate_schedule
 from ..csrc import ops
@@ -77,10 +78,21 @@ class DecoderModel:
                    and (l.feed_forward is None or getattr(l.feed_forward, "graph_safe", False)) for l in self.layers)
 
     def cache_requests(self) -> Dict[int, List[object]]:
+        """What every cache entry keeps: its writer's requests.  A run that only reads an entry may reach further back
+        than the writer does; the entry then keeps keys for the widest window among its readers and writer."""
         out: Dict[int, List[object]] = {}
         for e in self.spec.schedule:
             if e.writes_cache:
                 out[e.cache] = self.layers[e.layer].cache_requests()
+        for e in self.spec.schedule:
+            if e.writes_cache:
+                continue
+            for r in self.layers[e.layer].cache_requests():
+                if not isinstance(r, KVRequest):
+                    continue
+                for n, have in enumerate(out[e.cache]):
+                    if isinstance(have, KVRequest) and have.window is not None and (r.window is None or r.window > have.window):
+                        out[e.cache][n] = dataclasses.replace(have, window=r.window)
         return out
 
     def forward(self, ctx, cache: SequenceCache) -> Optional[torch.Tensor]:

@@ -22,8 +22,12 @@ Options a spec may give (all off by default):
   of ``taps`` positions per sequence beside its pages (``StateRequest``).
 * ``qk_norm: "projection"`` with the tensors ``q_norm``, ``k_norm``: q and k are RMS-normed over their whole
   projections (all heads at once, ``norm_eps`` inside the root) with weights of that size, before the rotation.
+  ``qk_norm: "head"``: every head is normed over its own values with one weight of the head's size that all heads share.
 * ``head_gate`` with the tensor ``g`` [n_heads, hidden]: every head's result is multiplied by the sigmoid of one
-  number per head, a projection of the mixer's input, before the output projection.
+  number per head, a projection of the mixer's input, before the output projection.  ``head_gate: "wide"``: the gate has
+  one number per value, ``g`` is [n_heads * v_head_dim, hidden].
+* ``sink``: the softmax's denominator counts one more key of score 0 that carries no value: the weights are
+  exp(s_j) / (1 + sum exp(s_j)), so a query may attend to nothing.
 * a position part whose cos and sin carry a constant factor (``magnitude``).
 
 With one of the last three the mixer runs "wide": one product gives [q | k | v | g] in float, one kernel norms, rotates
@@ -58,10 +62,11 @@ class Attention:
         out = {w["q"]: TensorReq((nh * hd, d)), w["k"]: TensorReq((nkv * hd, d)),
                w["v"]: TensorReq((nkv * hdv, d)), w["o"]: TensorReq((d, nh * hdv))}
         if spec.get("qk_norm"):
-            out[w["q_norm"]] = TensorReq((nh * hd,), init="ones")
-            out[w["k_norm"]] = TensorReq((nkv * hd,), init="ones")
+            per_head = spec.get("qk_norm") == "head"
+            out[w["q_norm"]] = TensorReq((hd if per_head else nh * hd,), init="ones")
+            out[w["k_norm"]] = TensorReq((hd if per_head else nkv * hd,), init="ones")
         if spec.get("head_gate"):
-            out[w["g"]] = TensorReq((nh, d))
+            out[w["g"]] = TensorReq((nh * hdv if spec.get("head_gate") == "wide" else nh, d))
         taps = spec.get("conv_taps") or 0
         if taps:
             # taps around 1/taps: the convolution keeps the projections' scale
@@ -93,10 +98,13 @@ class Attention:
         w = spec.weights
         wq, wk = tensors[w["q"]], tensors[w["k"]]
         qk_norm = spec.get("qk_norm")
-        if qk_norm not in (None, "projection"):
-            raise ValueError(f"attention: qk_norm {qk_norm!r} is not supported (projection)")
+        if qk_norm not in (None, "projection", "head"):
+            raise ValueError(f"attention: qk_norm {qk_norm!r} is not supported (projection, head)")
+        self.norm_per_head = qk_norm == "head"
         self.head_gate = bool(spec.get("head_gate"))
-        self.wide = bool(qk_norm or self.head_gate or (position is not None and getattr(position, "magnitude", 1.0) != 1.0)
+        self.gate_wide = spec.get("head_gate") == "wide"
+        self.sink = bool(spec.get("sink"))
+        self.wide = bool(qk_norm or self.head_gate or self.sink or (position is not None and getattr(position, "magnitude", 1.0) != 1.0)
                          or not standalone)
         if self.wide and self.conv_taps:
             raise ValueError("attention: a short convolution and the wide arrangement (qk_norm, head_gate) do not go together")
@@ -122,8 +130,8 @@ class Attention:
         self.k_off = self.n_heads * self.head_dim
         self.v_off = self.k_off + self.n_kv_heads * self.head_dim
         self.g_off = self.v_off + self.n_kv_heads * self.v_head_dim
-        self.n_in = self.g_off + (self.n_heads if self.head_gate else 0)
         self.n_mid = self.n_heads * self.v_head_dim
+        self.n_in = self.g_off + ((self.n_mid if self.gate_wide else self.n_heads) if self.head_gate else 0)
         if standalone:
             self.qkv = Linear(self._in, runtime)
             self.o = Linear([self._out], runtime)
@@ -154,9 +162,9 @@ class Attention:
         ops.norm_rope_append(p, 0, self.k_off, self.v_off, self.q_norm_w, self.k_norm_w, self.norm_eps, q, cache.k_pages,
                              cache.v_pages, ctx.token_seq, ctx.token_pos, table, pos.inv_freq if pos is not None else None,
                              getattr(pos, "magnitude", 1.0), self.n_heads, pos.rotary_dim if pos is not None else 0,
-                             self.pairing, writes_cache, rt.status)
-        att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt, self.softcap)
-        ops.head_gate(att, p if self.head_gate else None, self.g_off, mid, self.n_heads, mult)
+                             self.pairing, writes_cache, rt.status, per_head=self.norm_per_head)
+        att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt, self.softcap, sink=self.sink)
+        ops.head_gate(att, p if self.head_gate else None, self.g_off, mid, self.n_heads, mult, wide=self.gate_wide)
 
     def cache_requests(self) -> List[object]:
         v = self.v_head_dim if self.v_head_dim != self.head_dim else None
@@ -205,17 +213,17 @@ class Attention:
 
 
 def attend(q: torch.Tensor, cache: LayerCache, ctx, table: torch.Tensor, n_heads: int, scale: float, window: int,
-           rt: Runtime, softcap: float = 0.0) -> torch.Tensor:
+           rt: Runtime, softcap: float = 0.0, sink: bool = False) -> torch.Tensor:
     """Chooses the attention kernel: tensor-core kernels for bfloat16 when they take the
     head sizes, else the CUDA-core kernel (always for float32)."""
     if q.dtype == torch.bfloat16 and cache.v_pages.shape[3] == cache.k_pages.shape[3]:
         from ..csrc import attention_bf16
         out = attention_bf16.attend(q, cache.k_pages, cache.v_pages, ctx, table, n_heads, scale, window, rt.status,
-                                    softcap=softcap)
+                                    softcap=softcap, sink=sink)
         if out is not None:
             return out
     return ops.attention_simt(q, cache.k_pages, cache.v_pages, ctx.token_seq, ctx.token_pos, table, n_heads, scale,
-                              window, rt.status, softcap=softcap)
+                              window, rt.status, softcap=softcap, sink=sink)
 
 
 register_mixer("attention", Attention)

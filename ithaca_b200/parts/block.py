@@ -2,7 +2,11 @@
 
 ``prenorm``: x += mixer(norm(x)); x += feed_forward(norm(x)) -- the order of the
 reference's layer loop (src/model.cpp:1460-1565).  The residual stream is float32
-and the parts add into it, so the sum never passes through 16 bits.
+and the parts add into it, so the sum never passes through 16 bits.  With ``layer_scale`` in the record's
+parameters (``{"mixer": tensor name, "feed_forward": tensor name}``) each sublayer's result is multiplied element by element by
+a vector of the layer before it joins the stream: x += s1 * mixer(norm(x)); x += s2 * feed_forward(norm(x)).  The sublayer
+then writes into a float32 buffer of its own, and one kernel adds s1 times it to the stream and forms the feed-forward's
+norm of the new stream in the same pass.  Such a layer may have no feed-forward.
 
 ``sandwich``: a norm in front of and behind each sublayer, and a constant on what joins the
 stream: x += m * norm_out(mixer(norm(x))); x += m * norm_out'(feed_forward(norm'(x))).  The
@@ -25,7 +29,7 @@ from ..cache.cache import LayerCache
 from ..config.spec import BlockSpec
 from ..csrc import ops
 from ..weights.loader import TensorReq
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Runtime, register_block
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Runtime, as_float32, register_block
 
 
 def _merge(into: Dict[str, TensorReq], more: Mapping[str, TensorReq]) -> None:
@@ -40,15 +44,26 @@ class PreNormBlock:
     def manifest(cls, spec: BlockSpec) -> Dict[str, TensorReq]:
         out: Dict[str, TensorReq] = {}
         _merge(out, MIXERS.get(spec.mixer.kind).manifest(spec.mixer))
-        _merge(out, FEED_FORWARDS.get(spec.feed_forward.kind).manifest(spec.feed_forward))
-        for n in spec.norms.values():
+        if spec.feed_forward is not None:
+            _merge(out, FEED_FORWARDS.get(spec.feed_forward.kind).manifest(spec.feed_forward))
+        for name, n in spec.norms.items():
+            if spec.feed_forward is None and name == "feed_forward":
+                continue
             _merge(out, NORMS.get(n.kind).manifest(n))
         if spec.position is not None:
             _merge(out, POSITIONS.get(spec.position.kind).manifest(spec.position))
+        size = spec.norms["mixer"].get("size")
+        for sub, name in (spec.params.get("layer_scale") or {}).items():
+            if sub == "mixer" or spec.feed_forward is not None:
+                _merge(out, {name: TensorReq((size,), init="ones")})
         return out
 
     def __init__(self, spec: BlockSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
-        for need in ("mixer", "feed_forward"):
+        scales = spec.params.get("layer_scale")
+        has_ff = spec.feed_forward is not None
+        if not has_ff and scales is None:
+            raise ValueError("prenorm block: a layer without layer scale needs a feed-forward")
+        for need in ("mixer",) + (("feed_forward",) if has_ff else ()):
             if need not in spec.norms:
                 raise ValueError(f"prenorm block: the spec has no '{need}' norm")
         position = None
@@ -59,16 +74,36 @@ class PreNormBlock:
             self.mixer = mixer_cls(spec.mixer, tensors, runtime, position=position)
         else:
             self.mixer = mixer_cls(spec.mixer, tensors, runtime)
-        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, tensors, runtime)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, tensors, runtime) if has_ff else None
         self.mixer_norm = NORMS.get(spec.norms["mixer"].kind)(spec.norms["mixer"], tensors, runtime)
-        self.ff_norm = NORMS.get(spec.norms["feed_forward"].kind)(spec.norms["feed_forward"], tensors, runtime)
+        self.ff_norm = NORMS.get(spec.norms["feed_forward"].kind)(spec.norms["feed_forward"], tensors, runtime) if has_ff else None
+        self.runtime = runtime
+        self.scaled = scales is not None
+        if self.scaled:
+            for sub in ("mixer",) + (("feed_forward",) if has_ff else ()):
+                if sub not in scales:
+                    raise ValueError(f"prenorm block: layer_scale names no vector for the {sub}")
+            if has_ff and not (hasattr(self.ff_norm, "weight") and hasattr(self.ff_norm, "eps") and not hasattr(self.ff_norm, "bias")):
+                raise ValueError("prenorm block: with layer scale the feed-forward's norm must be an RMS norm")
+            self.mixer_scale = as_float32(tensors[scales["mixer"]], runtime)
+            self.ff_scale = as_float32(tensors[scales["feed_forward"]], runtime) if has_ff else None
 
     def cache_requests(self) -> List[object]:
         return list(self.mixer.cache_requests())
 
     def forward(self, residual: torch.Tensor, ctx, cache: LayerCache, writes_cache: bool = True) -> None:
-        self.mixer.forward(self.mixer_norm.forward(residual), ctx, cache, residual, writes_cache)
-        self.feed_forward.forward(self.ff_norm.forward(residual), ctx, residual)
+        if not self.scaled:
+            self.mixer.forward(self.mixer_norm.forward(residual), ctx, cache, residual, writes_cache)
+            self.feed_forward.forward(self.ff_norm.forward(residual), ctx, residual)
+            return
+        y = torch.empty_like(residual)
+        self.mixer.forward(self.mixer_norm.forward(residual), ctx, cache, y, writes_cache, accumulate=False)
+        if self.feed_forward is None:
+            ops.scale_add_norm(y, self.mixer_scale, residual)
+            return
+        xn = ops.scale_add_norm(y, self.mixer_scale, residual, self.ff_norm.weight, self.ff_norm.eps, self.runtime.act_dtype)
+        self.feed_forward.forward(xn, ctx, y, accumulate=False)
+        ops.scale_add_norm(y, self.ff_scale, residual)
 
 
 class SandwichBlock:

@@ -1,0 +1,105 @@
+"""The gated delta rule mixer.
+
+q = Wq x and k = Wk x (``n_qk_heads`` heads of ``head_dim``), v = Wv x (``n_heads`` heads of ``v_head_dim``); value head h uses
+q/k head h / (n_heads / n_qk_heads).  Each of q, k, v passes a short causal convolution over time per channel
+(``conv_taps`` taps, no bias; the last column of the stored [channels, taps] matrix meets the current token, zeros stand
+before the sequence's start) and silu.  q and k then become unit vectors per head, x / sqrt(sum x^2 + ``unit_eps``), and q
+is multiplied by head_dim^(-1/2).  Per token and value head a step b = sigmoid(Wb x) and a decay
+g = exp(-exp(A_log) * softplus(Wa x + dt_bias)).  Per head, with S of size head_dim x v_head_dim and zero before the
+sequence's first token:
+
+    S <- g S;    u = b (v - S^T k);    S <- S + k u^T;    o = S^T q
+
+so the read-out sees the current token's write.  Every head's o is RMS-normed over its values (``norm_eps`` inside the
+root) with one weight of size v_head_dim that the heads share, multiplied by silu(Wg x), and projected out.
+
+Per sequence and cache entry the mixer keeps S as float32 [2, heads, head_dim, v_head_dim] (two copies by the parity of
+the position the state belongs to, so that a decode step never overwrites what it read and may be run twice) and a ring
+of the last ``conv_taps`` inputs of the convolution, float32.  One product gives [q | k | v | g | b | a] in float; the
+convolution's result, the unit norms, steps, decays, the state and its sums are float32 on both paths; only the
+products' operands are 16-bit on the bfloat16 path.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Mapping
+
+import torch
+
+from ..cache.cache import LayerCache, StateRequest
+from ..config.spec import PartSpec
+from ..csrc import ops
+from ..weights.loader import TensorReq
+from .base import Runtime, as_float32, register_mixer
+from .linear import Linear
+
+STATE, RING = "delta_state", "delta_conv_ring"
+
+
+class GatedDeltaRule:
+    graph_safe = True       # slots, positions and lengths come from device arrays; state by parity, ring by position
+
+    @classmethod
+    def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
+        d, H, G, dk, dv, taps = (spec["hidden_size"], spec["n_heads"], spec["n_qk_heads"], spec["head_dim"], spec["v_head_dim"],
+                                 spec["conv_taps"])
+        w = spec.weights
+        return {w["q"]: TensorReq((G * dk, d)), w["k"]: TensorReq((G * dk, d)), w["v"]: TensorReq((H * dv, d)),
+                w["q_conv"]: TensorReq((G * dk, taps), std=1.0 / taps), w["k_conv"]: TensorReq((G * dk, taps), std=1.0 / taps),
+                w["v_conv"]: TensorReq((H * dv, taps), std=1.0 / taps), w["b"]: TensorReq((H, d)), w["a"]: TensorReq((H, d)),
+                w["A_log"]: TensorReq((H,), std=0.5), w["dt_bias"]: TensorReq((H,), std=0.5),
+                w["norm"]: TensorReq((dv,), init="ones"), w["g"]: TensorReq((H * dv, d)), w["o"]: TensorReq((d, H * dv))}
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        self.hidden = int(spec["hidden_size"])
+        self.n_heads = int(spec["n_heads"])
+        self.n_qk_heads = int(spec["n_qk_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.v_head_dim = int(spec["v_head_dim"])
+        self.taps = int(spec["conv_taps"])
+        self.norm_eps = float(spec["norm_eps"])
+        self.unit_eps = float(spec.get("unit_eps", 1e-6))
+        if self.n_heads % self.n_qk_heads:
+            raise ValueError(f"gated_delta: {self.n_heads} heads cannot share {self.n_qk_heads} query/key heads evenly")
+        if self.head_dim > 512:
+            raise ValueError(f"gated_delta: the kernel holds a state column's rows in the registers of up to 16 warps, 32 each; found {self.head_dim}")
+        if self.taps < 1:
+            raise ValueError("gated_delta: the convolution needs at least one tap")
+        H, G, dk, dv = self.n_heads, self.n_qk_heads, self.head_dim, self.v_head_dim
+        w = spec.weights
+        self.in_proj = Linear([tensors[w[r]] for r in ("q", "k", "v", "g", "b", "a")], runtime)
+        self.o = Linear([tensors[w["o"]]], runtime)
+        self.k_off = G * dk
+        self.v_off = 2 * G * dk
+        self.channels = 2 * G * dk + H * dv
+        self.g_off = self.channels
+        self.b_off = self.g_off + H * dv
+        self.a_off = self.b_off + H
+        cw = torch.cat([tensors[w[r]].to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")], dim=0)
+        self.conv_w = cw.to(runtime.device).t().contiguous()                  # tap-major [taps, channels]
+        self.A_log = as_float32(tensors[w["A_log"]], runtime)
+        self.dt_bias = as_float32(tensors[w["dt_bias"]], runtime)
+        self.norm_w = as_float32(tensors[w["norm"]], runtime)
+        self.runtime = runtime
+
+    def cache_requests(self) -> List[object]:
+        out: List[object] = [StateRequest(STATE, (2, self.n_heads, self.head_dim, self.v_head_dim), "float32")]
+        if self.taps > 1:
+            out.append(StateRequest(RING, (self.taps, self.channels), "float32"))
+        return out
+
+    def forward(self, x: torch.Tensor, ctx, cache: LayerCache, residual: torch.Tensor, writes_cache: bool = True,
+                accumulate: bool = True) -> None:
+        if not writes_cache:
+            raise ValueError("gated_delta: a run cannot read another run's state without advancing it")
+        rt, H, G, dk, dv = self.runtime, self.n_heads, self.n_qk_heads, self.head_dim, self.v_head_dim
+        p = self.in_proj(x, out_dtype=torch.float32)                           # [T, q | k | v | g | b | a]
+        ring = cache.state(RING) if self.taps > 1 else None
+        u = ops.causal_conv(p[:, :self.channels], self.conv_w, None, ring, ctx, torch.float32, act=True)
+        bg = ops.delta_prepare(u, 0, self.k_off, p, self.b_off, self.a_off, self.A_log, self.dt_bias, G, dk, H, dk ** -0.5,
+                               self.unit_eps)
+        o = ops.delta_rule(u, 0, self.k_off, self.v_off, bg, cache.state(STATE), ctx, H, G, dk, dv)
+        mid = ops.head_norm_gate(o, self.norm_w, self.norm_eps, p, self.g_off, H, rt.act_dtype, gate="silu")
+        self.o(mid, out=residual, accumulate=accumulate)
+
+
+register_mixer("gated_delta", GatedDeltaRule)

@@ -4,7 +4,10 @@ Gate and up are stacked into one product ([gate; up], the split the reference
 applies to a fused ``ffn_up``, src/model.cpp:1553-1557).
 
 ``activation: "swish"`` is the same arrangement with the gate's constants as parameters: g <- min(g, limit) and
-u <- clamp(u, -limit, limit) when ``limit`` is given, then h = g * sigmoid(alpha g) * (u + up_shift)."""
+u <- clamp(u, -limit, limit) when ``limit`` is given, then h = g * sigmoid(alpha g) * (u + up_shift).
+
+The ungated feed-forward (``mlp``): y = Wd act(Wu x) with ``activation`` ``relu2`` (the square of relu) or ``gelu_tanh``
+(0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), computed in float on the up product's float result."""
 from __future__ import annotations
 
 from typing import Dict, Mapping
@@ -58,4 +61,30 @@ class GatedMLP:
         self.down(h, out=residual, accumulate=accumulate)
 
 
+class PlainMLP:
+    graph_safe = True
+
+    @classmethod
+    def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
+        d, ff = spec["hidden_size"], spec["intermediate_size"]
+        w = spec.weights
+        return {w["up"]: TensorReq((ff, d)), w["down"]: TensorReq((d, ff))}
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        self.act = spec.get("activation", "relu2")
+        if self.act not in ops.PLAIN_ACTS:
+            raise ValueError(f"mlp: activation {self.act!r} is not supported ({', '.join(ops.PLAIN_ACTS)})")
+        self.hidden = int(spec["hidden_size"])
+        self.intermediate = int(spec["intermediate_size"])
+        w = spec.weights
+        self.up = Linear([tensors[w["up"]]], runtime)
+        self.down = Linear([tensors[w["down"]]], runtime)
+        self.runtime = runtime
+
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, accumulate: bool = True) -> None:
+        h = ops.plain_act(self.up(x, out_dtype=torch.float32), self.runtime.act_dtype, self.act)
+        self.down(h, out=residual, accumulate=accumulate)
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("mlp", PlainMLP)
