@@ -9,6 +9,9 @@
     python bench.py --only tiralix [--batch B]                  the Tiralix decoder (selective scan and parallel softmax / decayed linear
                                                                 attention layers) at a few sizes beside a Llama of equal width, heads,
                                                                 feed-forward and depth, in the same form
+    python bench.py --only mimadra [--batch B]                  the Mimadra decoder (gated delta rule, latent attention whose second layer
+                                                                reads the first one's rows, windowed attention with a sink) beside a
+                                                                Llama of equal width, heads, feed-forward and depth, in the same form
     python bench.py --config 1b-unequal|13b-long                the other two workloads alone, through Engine.generate
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
@@ -546,6 +549,47 @@ def tiralix_pair(size, vocab=32000):
     return tir, llama, len(kinds)
 
 
+MIMADRA_SIZES = [
+    # name, width, heads, kv heads, head size, feed-forward, latent rank, turning part, window, layers
+    ("2048 wide, 16 heads of 128, latent of 512 + 64", 2048, 16, 4, 128, 8192, 512, 64, 1024,
+     ("delta", "latent_attention", "latent_shared", "attention", "delta")),
+    ("4096 wide, 32 heads of 128, latent of 512 + 64", 4096, 32, 8, 128, 14336, 512, 64, 2048,
+     ("delta", "latent_attention", "latent_shared", "attention")),
+]
+
+
+def mimadra_pair(size, vocab=32000):
+    """The Mimadra configuration of a size and the Llama next to it: the same width, heads, head size, feed-forward width,
+    window and number of layers."""
+    _, d, nh, nkv, hd, ff, rank, rd, window, kinds = size
+    rot = {"base": 500000.0, "dims": rd}
+    mixers = {
+        "delta": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "conv": 4},
+        "attention": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window},
+                      "rot": {"base": 500000.0, "dims": hd // 2}},
+        "latent_attention": {"heads": nh, "dim": hd, "rot_dim": rd, "vdim": hd, "kv_rank": rank, "scale": (hd + rd) ** -0.5,
+                             "mask": {"size": window}, "rot": rot},
+    }
+    layers, first_latent = [], None
+    for i, k in enumerate(kinds):
+        m = dict(mixers["latent_attention" if k == "latent_shared" else k])
+        if k == "latent_attention" and first_latent is None:
+            first_latent = i
+        if k == "latent_shared":
+            m["kv_from"] = first_latent
+        layers.append({"type": "latent_attention" if k == "latent_shared" else k, "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+    mim = {"architecture": "Mimadra", "vocab": vocab, "width": d, "norm": {"eps": 1e-6}, "logit_softcap": 25.0, "layers": layers}
+    llama = {"architectures": ["LlamaForCausalLM"], "hidden_size": d, "num_hidden_layers": len(kinds), "num_attention_heads": nh,
+             "num_key_value_heads": nkv, "head_dim": hd, "intermediate_size": ff, "vocab_size": vocab, "rope_theta": 500000.0,
+             "rope_scaling": None, "rms_norm_eps": 1e-6, "max_position_embeddings": 131072, "tie_word_embeddings": False,
+             "torch_dtype": "bfloat16", "sliding_window": window, "use_sliding_window": True}
+    return mim, llama, len(kinds)
+
+
+def mimadra_run(pk, batch, steps, warmup, context=2048, prompt=4096):
+    return vebisun_run(pk, batch, steps, warmup, context, prompt, sizes=MIMADRA_SIZES, pair=mimadra_pair, name="mimadra")
+
+
 def tiralix_run(pk, batch, steps, warmup, context=2048, prompt=4096):
     return vebisun_run(pk, batch, steps, warmup, context, prompt, sizes=TIRALIX_SIZES, pair=tiralix_pair, name="tiralix")
 
@@ -642,7 +686,7 @@ def main():
                     help="with --only decode / prefill: another context length (decode) or prompt length (prefill) than the default run's")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate", "vebisun", "tiralix"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate", "vebisun", "tiralix", "mimadra"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -671,6 +715,9 @@ def main():
         return 0
     if args.only == "tiralix":
         print(json.dumps({"only": "tiralix", "peaks": pk, "sizes": tiralix_run(pk, args.batch, min(args.steps, 64), args.warmup)}))
+        return 0
+    if args.only == "mimadra":
+        print(json.dumps({"only": "mimadra", "peaks": pk, "sizes": mimadra_run(pk, args.batch, min(args.steps, 64), args.warmup)}))
         return 0
     if args.only == "issue-rate":
         # what the thread that issues tensor-core products costs: cycles per instruction, one or two issuing threads

@@ -51,9 +51,10 @@ def softplus(x: torch.Tensor) -> torch.Tensor:
 
 
 def _angles(positions: Sequence[int], r: int, base: float, dtype) -> torch.Tensor:
-    p = torch.tensor(list(positions), dtype=dtype)[:, None]
-    f = torch.tensor([float(base) ** (-2.0 * i / r) for i in range(r // 2)], dtype=dtype)[None, :]
-    return p * f                                                   # [T, r/2]
+    # the design forms positions and angles in 32-bit: the frequency is rounded to float32 and so is the product
+    p = torch.tensor(list(positions), dtype=torch.float32)[:, None]
+    f = torch.tensor([float(base) ** (-2.0 * i / r) for i in range(r // 2)], dtype=torch.float64).to(torch.float32)[None, :]
+    return (p * f).to(dtype)                                       # [T, r/2]
 
 
 def rotate_halves(x: torch.Tensor, positions: Sequence[int], r: int, base: float) -> torch.Tensor:
