@@ -254,6 +254,43 @@ def test_attention_with_a_sink(dtype, nh, nkv, hd, hdv, window, sink):
         assert rel_err(free.numpy(), want.numpy()) > 0.1                     # the sink matters here
 
 
+@pytest.mark.parametrize("nh,nkv,hd,kind,window", [(4, 2, 16, "mma", 33), (2, 2, 32, "mma", 0), (4, 2, 64, "tc", 70), (8, 2, 128, "tc", 130),
+                                                   (2, 1, 128, "mma", 64), (3, 3, 64, "tc", 0)])
+def test_tensor_core_attention_with_a_sink(nh, nkv, hd, kind, window):
+    """The bfloat16 kernels, prompts' portions (both kernels) and single tokens (chunks of one and of four pages): the sink
+    joins the running maximum and sum once, however many pages and chunks a query's keys span."""
+    from test_kernels_gpu import Paged
+    from ithaca_b200.csrc import attention_bf16 as A
+    i32 = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    lens = [1, 70, 200, 129, 64, 700]
+    g = torch.Generator().manual_seed(hd + window)
+    ks = [torch.randn(l, nkv, hd, generator=g) for l in lens]
+    vs = [torch.randn(l, nkv, hd, generator=g) for l in lens]
+    qs = [torch.randn(l, nh, hd, generator=g) * torch.linspace(0.05, 3.0, l)[:, None, None] for l in lens]
+    pk, pv = Paged(lens, nkv, hd, torch.bfloat16, 3), Paged(lens, nkv, hd, torch.bfloat16, 3)
+    pk.fill(ks, ks)
+    pv.fill(vs, vs)
+    k_d, v_d, tab = pk.dev()[0], pv.dev()[0], pk.dev()[2]
+    rt = lambda a: a.bfloat16().double()
+    full = [P.windowed_attention(rt(qs[b]), rt(ks[b]), rt(vs[b]), 0.3, window or None, True) for b in range(len(lens))]
+    free = [P.windowed_attention(rt(qs[b]), rt(ks[b]), rt(vs[b]), 0.3, window or None, False) for b in range(len(lens))]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for new in ([1, 70, 67, 129, 5, 450], [1] * len(lens)):
+        q = torch.cat([a[l - n:] for a, l, n in zip(qs, lens, new)]).reshape(sum(new), nh * hd).bfloat16().to(DEV)
+        want = torch.cat([a[l - n:] for a, l, n in zip(full, lens, new)]).reshape(sum(new), -1).numpy()
+        other = torch.cat([a[l - n:] for a, l, n in zip(free, lens, new)]).reshape(sum(new), -1).numpy()
+        assert rel_err(other, want) > 0.1                                        # the sink matters here
+        if max(new) > 1:
+            got = [A.prefill(q, k_d, v_d, i32(np.concatenate([[0], np.cumsum(new)])), i32(lens), tab, len(lens), max(new), nh, 0.3,
+                             window, status, kind=kind, sink=True)]
+        else:
+            got = [A.decode(q, k_d, v_d, i32(lens), tab, len(lens), max(lens), nh, 0.3, window, status, chunk_pages=c, sink=True)
+                   for c in (1, 4)]
+        assert status.item() == 0
+        for o in got:
+            assert rel_err(o.float().cpu().numpy(), want) < 8e-3
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gate_per_value_kernel(dtype):
     from ithaca_b200.csrc import ops
