@@ -24,7 +24,7 @@ import torch
 
 from ..cache.cache import KVRequest, LayerCache
 from ..config.spec import PartSpec
-from ..csrc import ops
+from ..csrc import attention_latent, ops
 from ..weights.loader import TensorReq
 from .base import Runtime, as_float32, register_mixer, to_device
 from .linear import Linear
@@ -102,8 +102,11 @@ class LatentAttention:
         ops.latent_prepare(p, 0, self.c_off, self.c_norm_w, self.norm_eps, q_plain, q_full, cache.k_pages, ctx.token_seq,
                            ctx.token_pos, table, self.position.inv_freq, H, dk, dr, rank, writes_cache, rt.status)
         ops.gemm_heads(q_plain.view(T, H, dk), self.uk_t, q_full.view(T, H, hd)[:, :, :rank])
-        att = ops.attention_simt(q_full, cache.k_pages, None, ctx.token_seq, ctx.token_pos, table, H, self.scale,
-                                 self.window or 0, rt.status, values_in_keys=rank)                   # [T, H * rank]
+        # [T, H * rank]: the tensor-core kernel whose tile rows are the heads, or (32-bit, other sizes) the CUDA cores
+        att = attention_latent.attend(q_full, cache.k_pages, ctx, table, H, self.scale, self.window or 0, rt.status, rank)
+        if att is None:
+            att = ops.attention_simt(q_full, cache.k_pages, None, ctx.token_seq, ctx.token_pos, table, H, self.scale,
+                                     self.window or 0, rt.status, values_in_keys=rank)
         heads = torch.empty((T, H * dv), dtype=rt.act_dtype, device=x.device)
         ops.gemm_heads(att.view(T, H, rank), self.uv, heads.view(T, H, dv))
         if self.gate:

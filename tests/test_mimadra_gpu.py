@@ -73,7 +73,18 @@ CFG_B = {
         {"type": "latent_attention", "mixer": _lat(1, 32, 2, 8, 16, 0.25, 50.0), "mlp": None},
     ],
 }
-CONFIGS = {"A": CFG_A, "B": CFG_B}
+# latents wide enough for the kernel whose tile rows are the heads (bfloat16): five heads (rows of two tokens share a tile),
+# a reader with forty heads (more than one tile of heads) and a window of its own, a latent layer without a window
+CFG_C = {
+    "architecture": "Mimadra", "vocab": 89, "width": 64, "norm": {"eps": 1e-5}, "logit_softcap": 12.0,
+    "layers": [
+        {"type": "latent_attention", "mixer": _lat(5, 16, 16, 24, 64, 0.2, 1000.0, window=70), "mlp": _ff(72)},
+        {"type": "latent_attention", "mixer": _lat(40, 8, 16, 8, 64, 0.3, 1000.0, window=129, kv_from=0), "mlp": None},
+        {"type": "delta", "mixer": _delta(2, 1, 16, 32, 2), "mlp": _ff(48)},
+        {"type": "latent_attention", "mixer": _lat(2, 32, 32, 16, 128, 0.15, 10000.0), "mlp": _ff(40)},
+    ],
+}
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
 
 
 def make_tensors(cfg, seed):
@@ -291,6 +302,45 @@ def test_tensor_core_attention_with_a_sink(nh, nkv, hd, kind, window):
             assert rel_err(o.float().cpu().numpy(), want) < 8e-3
 
 
+@pytest.mark.parametrize("nh,nkv,hd,hdv,window,sink", [(16, 1, 80, 64, 0, False), (3, 1, 80, 64, 70, False), (40, 1, 96, 64, 130, False),
+                                                       (8, 2, 144, 128, 33, True), (5, 1, 64, 64, 64, False), (1, 1, 208, 192, 2, False)])
+def test_attention_over_rows_that_hold_their_values(nh, nkv, hd, hdv, window, sink):
+    """The bfloat16 kernel whose tile rows are (token, head) pairs of one key/value head: portions and single tokens over
+    scrambled pages, few heads (several tokens in a tile), many (several tiles of heads), and single tokens of few
+    sequences, whose pages are cut into runs that a second kernel merges."""
+    from test_kernels_gpu import Paged
+    from ithaca_b200.csrc import attention_latent as L
+    i32 = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    lens = [1, 70, 200, 129, 64, 700]
+    g = torch.Generator().manual_seed(hd + window)
+    ks = [torch.randn(l, nkv, hd, generator=g) for l in lens]
+    qs = [torch.randn(l, nh, hd, generator=g) * torch.linspace(0.05, 1.5, l)[:, None, None] for l in lens]
+    pk = Paged(lens, nkv, hd, torch.bfloat16, 3)
+    pk.fill(ks, ks)
+    k_d, tab = pk.dev()[0], pk.dev()[2]
+    rt = lambda a: a.bfloat16().double()
+    full = [P.windowed_attention(rt(qs[b]), rt(ks[b]), rt(ks[b])[:, :, :hdv], 0.2, window or None, sink) for b in range(len(lens))]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    assert L.supported(hd, hdv)
+    for new in ([1, 70, 67, 129, 5, 450], [1] * len(lens)):
+        q = torch.cat([a[l - n:] for a, l, n in zip(qs, lens, new)]).reshape(sum(new), nh * hd).bfloat16().to(DEV)
+        want = torch.cat([a[l - n:] for a, l, n in zip(full, lens, new)]).reshape(sum(new), -1).numpy()
+        ctx = SimpleNamespace(n_seqs=len(lens), max_new=max(new), kv_len_bound=max(lens), max_kv_len=max(lens), kv_lens=i32(lens),
+                              cu_seqlens=i32(np.concatenate([[0], np.cumsum(new)])), host_n_new=new, host_kv_lens=lens)
+        got = L.attend(q, k_d, ctx, tab, nh, 0.2, window, status, hdv, sink=sink)
+        assert status.item() == 0
+        assert rel_err(got.float().cpu().numpy(), want) < 8e-3, new[:2]
+    # one long sequence alone: its pages are cut into many runs
+    chunk, n = L.splits_for(1, 11)
+    assert n > 1 and chunk * n >= 11
+    b = len(lens) - 1
+    ctx = SimpleNamespace(n_seqs=1, max_new=1, kv_len_bound=lens[b], max_kv_len=lens[b], kv_lens=i32([lens[b]]), cu_seqlens=i32([0, 1]),
+                          host_n_new=[1], host_kv_lens=[lens[b]])
+    got = L.attend(qs[b][-1:].reshape(1, nh * hd).bfloat16().to(DEV), k_d, ctx, tab[b:b + 1].contiguous(), nh, 0.2, window, status, hdv, sink=sink)
+    assert status.item() == 0
+    assert rel_err(got.float().cpu().numpy(), full[b][-1:].reshape(1, -1).numpy()) < 8e-3
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gate_per_value_kernel(dtype):
     from ithaca_b200.csrc import ops
@@ -380,6 +430,7 @@ ONE_LAYER = {
     "delta": _one_layer("delta", _delta(4, 2, 16, 24, 4)),
     "delta, one tap": _one_layer("delta", _delta(2, 2, 48, 8, 1), mlp=_ff(40)),
     "latent": _one_layer("latent_attention", _lat(3, 16, 8, 24, 32, 0.2, 250.0, window=37)),
+    "latent, a wide one": _one_layer("latent_attention", _lat(5, 16, 16, 24, 64, 0.2, 250.0, window=75)),
     "latent, no window": _one_layer("latent_attention", _lat(2, 24, 4, 8, 20, 0.3, 10000.0), mlp=_ff(24)),
 }
 
@@ -401,7 +452,7 @@ def test_one_layer_models(tmp_path, which, dtype):
 
 # ------------------------------------------------------------------------------------------ whole models
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_schedules_against_the_plain_model(models, name, dtype):
     from ithaca_b200 import Engine
     d, t = models[name]
