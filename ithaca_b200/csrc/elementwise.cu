@@ -233,10 +233,7 @@ IK_EXPORT int ik_scale_add_norm(const float* y, const float* scale, float* resid
 
 // ------------------------------------------------------------------ activation of an ungated feed-forward
 // kind 0: relu(x)^2;  kind 1: gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).
-__device__ __forceinline__ float ik_plain_act_value(float x, int kind) {
-    if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
-    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-}
+// (ik_plain_act_value: common.cuh, shared with the products' epilogues)
 template <typename TO>
 __global__ void plain_act_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t total, int kind) {
     ik_pdl_wait();

@@ -41,6 +41,19 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, a
     return out
 
 
+def gemm_act(x: torch.Tensor, w: torch.Tensor, act: str, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """h = act(x W^T) in one kernel, ``act`` one of ``ops.PLAIN_ACTS``: the product's epilogue applies it to its float
+    sums, so the [tokens, ff] float intermediate is never written."""
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
+    if takes_skinny(x.shape[0], w.shape[0], w.shape[1]):
+        done = ops.gemm_bf16_mma(x, w, out=out, kind=1, act=act)
+    else:
+        done = ops.gemm_tcgen05(x, w, out=out, status=ops.device_status(x.device), act=act)
+    if done is None:
+        return ops.plain_act(ops.gemm_simt(x, w, out_dtype=torch.float32), out_dtype, act)
+    return out
+
+
 def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, glu=None) -> torch.Tensor:
     """h = silu(x Wg^T) * (x Wu^T) in one kernel.  ``w_interleaved``: [2 ff, d] with gate j in row 2j and
     up j in row 2j + 1, so that a product tile holds both halves of every pair it covers and the

@@ -181,7 +181,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __r
         float s = 0.f;
         #pragma unroll
         for (int w = 0; w < 8; w++) s += red[(size_t)w * R * COLS + row * COLS + m];
-        store_out(Y, (size_t)m * ldy + n0 + row, s, accumulate);
+        store_out(Y, (size_t)m * ldy + n0 + row, ik_glu_act(swiglu, s), accumulate);
     }
 }
 
@@ -222,10 +222,14 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool va
 template <typename TY>
 __global__ void __launch_bounds__(256)
 gemm_tiled_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, TY* __restrict__ Y,
-                  int M, int N, int K, int ldx, int ldw, int ldy, int accumulate) {
+                  int M, int N, int K, int ldx, int ldw, int ldy, int accumulate, long long bx, long long bw, long long by) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     ik_pdl_wait();
     ik_pdl_launch_dependents();
+    // a batch of products in one launch: product z reads X + z bx and W + z bw and writes Y + z by (elements)
+    X += (size_t)blockIdx.z * bx;
+    W += (size_t)blockIdx.z * bw;
+    Y += (size_t)blockIdx.z * by;
     __nv_bfloat16* xs = (__nv_bfloat16*)smem_raw;                         // [STAGES][TBM][TBK]
     __nv_bfloat16* ws = xs + (size_t)STAGES * TBM * TBK;                  // [STAGES][TBN][TBK]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -298,14 +302,14 @@ gemm_tiled_kernel(const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __re
 
 template <typename TY>
 int launch_tiled(const void* X, const void* W, void* Y, int M, int N, int K, int ldx, int ldw, int ldy, int accumulate,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, int batch = 1, long long bx = 0, long long bw = 0, long long by = 0) {
     const size_t smem = (size_t)STAGES * (TBM + TBN) * TBK * sizeof(__nv_bfloat16);
     auto kern = gemm_tiled_kernel<TY>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    dim3 grid((N + TBN - 1) / TBN, (M + TBM - 1) / TBM);
+    dim3 grid((N + TBN - 1) / TBN, (M + TBM - 1) / TBM, batch);
     IK_RETURN_IF_ERROR(ik_launch(kern, grid, 256, smem, stream, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (TY*)Y, M, N, K, ldx, ldw, ldy,
-                                      accumulate));
+                                      accumulate, bx, bw, by));
     IK_LAUNCH_STATUS();
 }
 
@@ -322,9 +326,11 @@ static int gemm_bf16_mma_impl(const void* X, const void* W, void* Y, int y_dtype
     if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N))) return IK_BAD_ARGUMENT;
     if (swiglu && ((N & 1) || accumulate || kind == 2 || (kind == 0 && M > 64))) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+    if (swiglu.act && (accumulate || rope.q_out)) return IK_BAD_ARGUMENT;
     if (!aligned_ok(X, W, K, ldx, ldw)) return IK_UNSUPPORTED;
     if (M == 0) return IK_OK;
     const bool skinny = kind == 1 || (kind == 0 && M <= 64);
+    if (swiglu.act && !skinny) return IK_UNSUPPORTED;          // the activation is the skinny kernel's epilogue only
     if (skinny && M > 64) return IK_UNSUPPORTED;
 #define IK_SK(NT, U)                                                                                           \
     return y_dtype == IK_F32 ? launch_skinny<NT, U, float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, swiglu, rope, stream) \
@@ -343,6 +349,18 @@ static int gemm_bf16_mma_impl(const void* X, const void* W, void* Y, int y_dtype
 #undef IK_SK
     return y_dtype == IK_F32 ? launch_tiled<float>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream)
                              : launch_tiled<__nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, accumulate, stream);
+}
+
+// One product per batch entry in one launch (the tiled kernel): entry z multiplies X + z bx [M, K] (row stride ldx) by
+// W + z bw [N, K] into Y + z by (strides in elements).  Heads of one tensor are a batch whose stride is a head's width.
+IK_EXPORT int ik_gemm_bf16_mma_batched(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw,
+                                       int ldy, int batch, long long bx, long long bw, long long by, cudaStream_t stream) {
+    if (M < 0 || N <= 0 || K <= 0 || batch <= 0 || batch > 65535 || ldx < K || ldw < K || ldy < N) return IK_BAD_ARGUMENT;
+    if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+    if (!aligned_ok(X, W, K, ldx, ldw) || bx % 8 || bw % 8) return IK_UNSUPPORTED;
+    if (M == 0) return IK_OK;
+    return y_dtype == IK_F32 ? launch_tiled<float>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream, batch, bx, bw, by)
+                             : launch_tiled<__nv_bfloat16>(X, W, Y, M, N, K, ldx, ldw, ldy, 0, stream, batch, bx, bw, by);
 }
 
 // swiglu: 0 = none, 1 = silu(gate) * up, 2 = gate * sigmoid(alpha gate) * (up + shift) with gate and up limited (common.cuh).

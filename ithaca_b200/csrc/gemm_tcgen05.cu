@@ -545,7 +545,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             }
                             #pragma unroll
                             for (int c = 0; c < 16; c++)
-                                if (m0 + c0 + 16 * h + c < M) ik_st(Y, (size_t)(m0 + c0 + 16 * h + c) * ldy + feature, v[16 * h + c]);
+                                if (m0 + c0 + 16 * h + c < M) ik_st(Y, (size_t)(m0 + c0 + 16 * h + c) * ldy + feature, ik_glu_act(swiglu, v[16 * h + c]));
                         }
                     }
                 }
@@ -616,7 +616,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         }
                         #pragma unroll
                         for (int c = 0; c < 16; c++)
-                            if (m0 + c0 + c < M) ik_st(Y, (size_t)(m0 + c0 + c) * ldy + feature, v[c]);
+                            if (m0 + c0 + c < M) ik_st(Y, (size_t)(m0 + c0 + c) * ldy + feature, ik_glu_act(swiglu, v[c]));
                     }
                 }
             }
@@ -681,7 +681,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, TY* __re
         const size_t m = idx / N, n = idx - m * N;
         const size_t o = m * ldy + n;
         if (accumulate) s += ik_ld(Y, o);
-        ik_st(Y, o, s);
+        ik_st(Y, o, ik_glu_act(swiglu, s));
     }
 }
 
@@ -823,7 +823,7 @@ int launch_pairs(const CUtensorMap& mw, const CUtensorMap& mx_half, void* Y, int
 int pairs_impl(const void* X, const void* W, void* Y, int y_dtype, int M, int N, int K, int ldx, int ldw, int ldy,
                int accumulate, IkGlu swiglu, int* status, const IkRopeStore& rope, cudaStream_t stream) {
     if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N))) return IK_BAD_ARGUMENT;
-    if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
+    if ((swiglu && ((N & 1) || accumulate)) || (swiglu.act && (accumulate || rope.q_out))) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
     if (M <= 256) return IK_UNSUPPORTED;                 // fewer tokens are bound by the weights' bytes: nothing to share
@@ -869,7 +869,7 @@ static int gemm_tcgen05_impl(const void* X, const void* W, void* Y, int y_dtype,
                              int bn_given = 0) {
     if (M < 0 || N <= 0 || K <= 0 || ldx < K || ldw < K || (!rope.q_out && ldy < (swiglu ? N / 2 : N)))
         return IK_BAD_ARGUMENT;
-    if (swiglu && ((N & 1) || accumulate)) return IK_BAD_ARGUMENT;
+    if ((swiglu && ((N & 1) || accumulate)) || (swiglu.act && (accumulate || rope.q_out))) return IK_BAD_ARGUMENT;
     if (y_dtype != IK_F32 && y_dtype != IK_BF16) return IK_BAD_ARGUMENT;
     if (K % 8 || ldx % 8 || ldw % 8 || ((uintptr_t)X % 16) || ((uintptr_t)W % 16)) return IK_UNSUPPORTED;
     if (splits != 1 && splits >= 0 && !partial) return IK_BAD_ARGUMENT;

@@ -76,6 +76,7 @@ _SIGNATURES = {
     "ik_copy": [_vp, _vp, _u64, _vp],
     "ik_rope_append": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_simt": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_gemm_bf16_mma_batched": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, _vp],
     "ik_gemm_bf16_mma": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f, _vp],
     "ik_gemm_tcgen05": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _f, _f, _i, _vp, _vp],
     "ik_gemm_tcgen05_tile": [_i],
@@ -347,8 +348,18 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+def _act_code(act: Optional[str], joins: bool = False) -> int:
+    """What a product's epilogue is told when it applies an ungated activation to every result (``PLAIN_ACTS``): 16 + its
+    number; 0 = none.  Not together with a gate/up join."""
+    if act is None:
+        return 0
+    if joins:
+        raise KernelError("gemm: an activation on every result and a gate/up join exclude each other")
+    return 16 + PLAIN_ACTS[act]
+
+
 def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
-                  accumulate: bool = False, kind: int = 0, swiglu: bool = False, glu=None) -> Optional[torch.Tensor]:
+                  accumulate: bool = False, kind: int = 0, swiglu: bool = False, glu=None, act: Optional[str] = None) -> Optional[torch.Tensor]:
     """bfloat16 operands, float accumulation on the warp-level tensor-core path.  ``kind``: 0 = by
     M, 1 = the skinny (decode) kernel, 2 = the tiled kernel.  Returns None when the kernels
     do not take these sizes (K not a multiple of 8, unaligned rows).  ``glu`` = (alpha, limit, shift) with ``swiglu``: the
@@ -370,10 +381,11 @@ def gemm_bf16_mma(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
     _need(out, "out", contiguous=False)
     if out.shape != (M, n_out) or out.stride(1) != 1:
         raise KernelError("gemm: the output has the wrong shape")
-    _work(f"gemm_skinny{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
+    _work(f"gemm_skinny{' +swiglu' if swiglu else ''}{' +' + act if act else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
     ga, gl, gs = glu if glu is not None else (1.0, 0.0, 0.0)
+    join = (2 if glu is not None else 1) if swiglu else _act_code(act, swiglu)
     st = lib().ik_gemm_bf16_mma(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
-                                out.stride(0), 1 if accumulate else 0, kind, (2 if glu is not None else 1) if swiglu else 0, ga, gl, gs,
+                                out.stride(0), 1 if accumulate else 0, kind, join, ga, gl, gs,
                                 _stream())
     if st == -2:
         return None
@@ -467,7 +479,7 @@ def pairs_lib():
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, out_dtype=torch.float32,
                  accumulate: bool = False, splits: Optional[int] = None,
                  status: Optional[torch.Tensor] = None, swiglu: bool = False, pairs: Optional[bool] = None,
-                 glu=None) -> Optional[torch.Tensor]:
+                 glu=None, act: Optional[str] = None) -> Optional[torch.Tensor]:
     """bfloat16 operands on the tcgen05 tensor cores (TMA-fed, accumulators in TMEM).  Returns None
     when the kernel does not take these sizes (K not a multiple of 8, unaligned rows).
 
@@ -491,14 +503,16 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
         raise KernelError("gemm: the output has the wrong shape")
     if splits is None:
         splits = tcgen05_splits(M, N, K)
-    join = (2 if glu is not None else 1) if swiglu else 0          # ``glu`` = (alpha, limit, shift): the gate with parameters
+    # ``glu`` = (alpha, limit, shift): the gate with parameters; ``act``: an ungated activation on every result
+    join = (2 if glu is not None else 1) if swiglu else _act_code(act, swiglu)
+    tag = (' +swiglu' if swiglu else '') + (' +' + act if act else '')
     ga, gl, gs = glu if glu is not None else (1.0, 0.0, 0.0)
     if splits == 1 and M > 256 and pairs is not False:
         pl = pairs_lib()
         if pl is None and pairs:
             raise KernelError("gemm_tcgen05: the pair mode was asked for but its library is not there")
         if pl is not None:
-            _work(f"gemm_tcgen05 pairs{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
+            _work(f"gemm_tcgen05 pairs{tag} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
             st = pl.ik_gemm_tcgen05_pairs(_ptr(x), _ptr(w), _ptr(out), _code(out), M, N, K, x.stride(0), w.stride(0),
                                           out.stride(0), 1 if accumulate else 0, join, ga, gl, gs, _ptr(status), _stream())
             if st != -2:
@@ -506,7 +520,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] =
                 return out
     partial = (stream_k_scratch(x.device) if splits == 0 else
                torch.empty((splits, M, N), dtype=torch.float32, device=x.device) if splits > 1 else None)
-    _work(f"gemm_tcgen05{' +swiglu' if swiglu else ''} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
+    _work(f"gemm_tcgen05{tag} {M}x{N}x{K}", 2 * (M * K + N * K) + M * n_out * out.element_size(), 2 * M * N * K)
     st = lib().ik_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(partial), M, N, K, x.stride(0),
                                w.stride(0), out.stride(0), 1 if accumulate else 0, join, ga, gl, gs, splits, _ptr(status),
                                _stream())
@@ -1193,6 +1207,13 @@ def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Ten
         raise KernelError("gemm_heads: the sizes do not fit together")
     N = w.shape[1]
     _work(f"gemm_heads {H}x{T}x{N}x{K}", _nbytes(w) + T * H * (K * x.element_size() + N * out.element_size()), 2 * T * H * N * K)
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        # the heads as a batch of the warp-level tensor-core product
+        st = lib().ik_gemm_bf16_mma_batched(_ptr(x), _ptr(w), _ptr(out), _code(out), T, N, K, x.stride(0), K, out.stride(0), H,
+                                            x.stride(1), N * K, out.stride(1), _stream())
+        if st != -2:
+            _check(st, "gemm_heads")
+            return out
     _check(lib().ik_gemm_simt_batched(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), T, N, K, x.stride(0), K, out.stride(0),
                                       H, x.stride(1), N * K, out.stride(1), _stream()), "gemm_heads")
     return out

@@ -82,7 +82,11 @@ class PlainMLP:
         self.runtime = runtime
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, accumulate: bool = True) -> None:
-        h = ops.plain_act(self.up(x, out_dtype=torch.float32), self.runtime.act_dtype, self.act)
+        if self.runtime.dtype == "bfloat16":
+            from ..csrc import gemm_bf16
+            h = gemm_bf16.gemm_act(x, self.up.weight, self.act, self.runtime.act_dtype)     # the activation is the product's epilogue
+        else:
+            h = ops.plain_act(self.up(x, out_dtype=torch.float32), self.runtime.act_dtype, self.act)
         self.down(h, out=residual, accumulate=accumulate)
 
 

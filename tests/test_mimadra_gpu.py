@@ -406,17 +406,34 @@ def test_head_norm_with_gate_kernel(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_products_per_head(dtype):
-    """One launch, one product per head, operands and results as column ranges of wider rows."""
+    """One launch, one product per head, operands and results as column ranges of wider rows; with 16-byte aligned heads
+    (the last three) the 16-bit operands go through the tensor cores."""
     from ithaca_b200.csrc import ops
     g = torch.Generator().manual_seed(5)
-    for T, H, K, N in ((70, 3, 16, 40), (5, 2, 40, 24), (130, 1, 33, 7)):
-        x = torch.randn(T, H, K + 4, generator=g).to(dtype)
+    for T, H, K, N, off, pad in ((70, 3, 16, 40, 2, 4), (5, 2, 40, 24, 2, 4), (130, 1, 33, 7, 2, 4), (200, 3, 32, 136, 8, 16),
+                                 (5, 2, 128, 64, 0, 0), (300, 5, 72, 130, 8, 8)):
+        x = torch.randn(T, H, K + pad, generator=g).to(dtype)
         w = torch.randn(H, N, K, generator=g).to(dtype)
         out = torch.zeros(T, H, N + 3, dtype=dtype, device=DEV)
-        ops.gemm_heads(x.to(DEV)[:, :, 2:2 + K], w.to(DEV), out[:, :, 1:1 + N])
-        want = torch.einsum("thk,hnk->thn", x[:, :, 2:2 + K].double(), w.double())
+        ops.gemm_heads(x.to(DEV)[:, :, off:off + K], w.to(DEV), out[:, :, 1:1 + N])
+        want = torch.einsum("thk,hnk->thn", x[:, :, off:off + K].double(), w.double())
         assert rel_err(out[:, :, 1:1 + N].float().cpu().numpy(), want.numpy()) < (2e-6 if dtype == torch.float32 else 8e-3)
         assert float(out[:, :, 0].abs().max()) == 0.0 and float(out[:, :, 1 + N:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("act", ["relu2", "gelu_tanh"])
+def test_activation_in_the_products_epilogue(act):
+    """act(x W^T) in one kernel for few tokens (the skinny kernel) and many (tcgen05: whole tiles, slices of K, pairs of
+    blocks), against the product in double with the activation applied to it."""
+    from ithaca_b200.csrc import gemm_bf16
+    g = torch.Generator().manual_seed(9)
+    for M, N, K in ((3, 200, 64), (12, 136, 256), (40, 72, 1024), (300, 520, 128), (700, 264, 192), (129, 2048, 64)):
+        x = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16()
+        w = torch.randn(N, K, generator=g).bfloat16()
+        got = gemm_bf16.gemm_act(x.to(DEV), w.to(DEV), act, torch.bfloat16)
+        z = x.double() @ w.double().T
+        want = torch.relu(z) ** 2 if act == "relu2" else 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+        assert rel_err(got.float().cpu().numpy(), want.numpy()) < 8e-3, (M, N, K)
 
 
 def _one_layer(kind, mixer, width=48, mlp=None):
