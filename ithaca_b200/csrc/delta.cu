@@ -4,8 +4,8 @@
 // Per value head h (its query and key come from head h / (H / G) of G query/key heads), with a decay g and a step b per
 // token and head:  S <- g S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q   (S is dk x dv, zero before the first token).
 // Both sums over rows are taken from the state as it was before the token: with A = S_old^T k and B = S_old^T q,
-// u = b (v - g A), S_new = g S_old + k u^T and o = g B + (k . q) u.  One pass over a thread's rows and one exchange
-// between the warps of a block per token.
+// u = b (v - g A), S_new = g S_old + k u^T and o = g B + (k . q) u.  One pass over a lane's rows and one exchange
+// between the lanes of a column per token.
 //
 // The step's tokens are token-major as everywhere: sequence n brings tokens cu_seqlens[n] .. cu_seqlens[n + 1] - 1 at
 // positions kv_lens[n] - count .. kv_lens[n] - 1, its state lies in slot slots[n], kept twice by the parity of the
@@ -17,6 +17,10 @@
 __device__ __forceinline__ void ik_cp_async4(float* dst, const float* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ik_cp_async16(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 __device__ __forceinline__ void ik_cp_async_wait_all() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
 
@@ -63,19 +67,27 @@ IK_EXPORT int ik_delta_prepare(float* u, int ldu, int q_off, int k_off, const fl
 }
 
 // ------------------------------------------------------------------ the rule
-// A block holds 32 columns of one head's state for one sequence; thread (j, part) keeps rows part*R .. part*R + R - 1 of
-// column j in registers, one warp per part.  Tokens come through shared memory in tiles of TT (q, k, the block's 32
-// values of v, the step and the decay), the next tile on its way (cp.async) while one is computed.  Per token every
-// thread forms its rows' share of A, B and k . q, the shares meet in shared memory (two copies by the token's parity,
-// so one barrier a token) and every thread adds them in part order.  What is computed for a token depends on its
-// sequence's earlier tokens only, not on where steps or tiles begin.  FULL: dk = parts * RMAX, a multiple of 4: no row
-// is guarded and q, k come from shared memory four at a time.
-template <int RMAX, bool FULL>
-__global__ void __launch_bounds__(512)
+// A column of the state is a recurrence of its own (u, the update and the read-out of column j use column j only), so the
+// work is cut by columns and no block-wide exchange is needed.  L lanes of a warp share one column, each keeping 16 of its
+// rows in registers (L = 1, 2, .. 32 for up to 16 L rows), the warp therefore holds 32 / L neighbouring columns, and up to
+// eight warps of a block hold neighbouring groups of columns of one head and one sequence.  Lane `part` owns the rows
+// 4 f .. 4 f + 3 of the four groups f = part, L + part, 2 L + part, 3 L + part: the lanes of a column then read
+// consecutive 16-byte words of q and k from shared memory.  Rows beyond dk are staged as zeros and stay zero in the state.
+//
+// Tokens come through shared memory in tiles of TT (q and k padded to 16 L rows, the block's values of v, the step, the
+// decay and k . q, which a warp forms once per token of a tile for all columns), the next tile on its way (cp.async)
+// while one is computed; there are two block barriers per tile and none per token.  Per token a lane forms its rows' share
+// of A and B in four running sums each, the shares of a column meet by shuffles between neighbouring lanes, and every lane
+// updates its rows.  What is computed for a token depends on its sequence's earlier tokens only, not on where steps or
+// tiles begin, and the sums run in the same order for a prompt and for a single token.
+constexpr int IK_DR_ROWS = 16;
+
+template <int L>
+__global__ void __launch_bounds__(256)
 delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, int v_off, const float* __restrict__ bg,
                   float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
-                  const int* __restrict__ kv_lens, float* __restrict__ out, int H, int G, int dk, int dv, int R, int TT, int W) {
-    extern __shared__ __align__(16) float sm[];          // [2][TT][W]: q, k, 32 of v, step, decay;  [2][parts][3][32] shares
+                  const int* __restrict__ kv_lens, float* __restrict__ out, int H, int G, int dk, int dv, int TT, int W, int vec) {
+    extern __shared__ __align__(16) float sm[];          // [2][TT][W]: q, k (16 L each), the block's v, step, decay, k . q
     ik_pdl_wait();
     IK_AFTER_WAIT(u);
     IK_AFTER_WAIT(bg);
@@ -83,37 +95,55 @@ delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
     IK_AFTER_WAIT(cu_seqlens);
     IK_AFTER_WAIT(kv_lens);
     ik_pdl_launch_dependents();
-    const int b = blockIdx.x, h = blockIdx.y, j = threadIdx.x, part = threadIdx.y, parts = blockDim.y;
-    const int col0 = blockIdx.z * 32, col = col0 + j;
+    constexpr int LR = L * IK_DR_ROWS, CPW = 32 / L;
+    const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
+    const int nwarps = nthreads >> 5, CB = nwarps * CPW;
+    const int part = lane % L, jj = lane / L;
+    const int col0 = blockIdx.z * CB, col = col0 + warp * CPW + jj;
     const bool live = col < dv;
     const int ccol = live ? col : dv - 1;
-    const int tid = part * 32 + j, nthreads = parts * 32, per_tile = TT * W;
-    float* shares = sm + 2 * per_tile;
+    const int per_tile = TT * W;
     const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1], end = kv_lens[b], start = end - (hi - lo);
     if (hi <= lo) return;
     const int kvh = h / (H / G);
     const size_t per = (size_t)H * dk * dv;
     const float* st_in = state + ((size_t)slots[b] * 2 + ((start - 1) & 1)) * per + (size_t)h * dk * dv;
     float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * per + (size_t)h * dk * dv;
-    float S[RMAX];
+    float S[IK_DR_ROWS];
     #pragma unroll
-    for (int r = 0; r < RMAX; r++) {
-        const int i = part * R + r;
-        S[r] = (r < R && i < dk && start > 0) ? st_in[(size_t)i * dv + ccol] : 0.f;
+    for (int r = 0; r < IK_DR_ROWS; r++) {
+        const int i = ((r >> 2) * L + part) * 4 + (r & 3);
+        S[r] = (i < dk && start > 0) ? st_in[(size_t)i * dv + ccol] : 0.f;
     }
     auto stage = [&](int t0, int buf) {
         const int n = min(TT, hi - t0);
-        for (int e = tid; e < n * W; e += nthreads) {
-            const int tt = e / W, w = e - tt * W;
+        for (int tt = 0; tt < n; tt++) {
             const float* row = u + (size_t)(t0 + tt) * ldu;
-            const float* src = nullptr;
-            if (w < dk) src = row + q_off + kvh * dk + w;
-            else if (w < 2 * dk) src = row + k_off + kvh * dk + (w - dk);
-            else if (w < 2 * dk + 32) { if (col0 + w - 2 * dk < dv) src = row + v_off + h * dv + col0 + (w - 2 * dk); }
-            else if (w < 2 * dk + 34) src = bg + ((size_t)(t0 + tt) * 2 + (w - 2 * dk - 32)) * H + h;
-            float* dst = sm + buf * per_tile + e;
-            if (src) ik_cp_async4(dst, src);
-            else *dst = 0.f;
+            float* dst = sm + buf * per_tile + tt * W;
+            const float* qs = row + q_off + kvh * dk;
+            const float* ks = row + k_off + kvh * dk;
+            if (vec) {                                   // dk a multiple of 4 and every row of q and k on a 16-byte boundary
+                for (int f = tid; f < 2 * (LR / 4); f += nthreads) {
+                    const int g4 = f < LR / 4 ? f : f - LR / 4;
+                    const float* src = (f < LR / 4 ? qs : ks) + 4 * g4;
+                    if (4 * g4 < dk) ik_cp_async16(dst + 4 * f, src);
+                    else *reinterpret_cast<float4*>(dst + 4 * f) = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            } else {
+                for (int w = tid; w < 2 * LR; w += nthreads) {
+                    const int i = w < LR ? w : w - LR;
+                    if (i < dk) ik_cp_async4(dst + w, (w < LR ? qs : ks) + i);
+                    else dst[w] = 0.f;
+                }
+            }
+            for (int w = tid; w < CB + 2; w += nthreads) {
+                if (w < CB) {
+                    if (col0 + w < dv) ik_cp_async4(dst + 2 * LR + w, row + v_off + h * dv + col0 + w);
+                    else dst[2 * LR + w] = 0.f;
+                } else {
+                    ik_cp_async4(dst + 2 * LR + w, bg + ((size_t)(t0 + tt) * 2 + (w - CB)) * H + h);
+                }
+            }
         }
     };
     stage(lo, 0);
@@ -123,70 +153,72 @@ delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
     for (int t0 = lo; t0 < hi; t0 += TT, buf ^= 1) {
         if (t0 + TT < hi) stage(t0 + TT, buf ^ 1);
         const int n_here = min(TT, hi - t0);
+        for (int tt = warp; tt < n_here; tt += nwarps) {        // k . q of the tile's tokens, lanes in index order, then the tree
+            float* x = sm + buf * per_tile + tt * W;
+            float c = 0.f;
+            for (int i = lane; i < LR; i += 32) c = fmaf(x[i], x[LR + i], c);
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+            if (lane == 0) x[2 * LR + CB + 2] = c;
+        }
+        __syncthreads();
         for (int tt = 0; tt < n_here; tt++) {
-            const float* q = sm + buf * per_tile + tt * W + part * R;
-            const float* k = q + dk;
-            const float* tail = sm + buf * per_tile + tt * W + 2 * dk;
-            const float v = tail[j], beta = tail[32], g = tail[33];
-            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f, c0 = 0.f;
-            if (FULL) {
-                #pragma unroll
-                for (int r = 0; r < RMAX; r += 4) {
-                    const float4 kk = *reinterpret_cast<const float4*>(k + r), qq = *reinterpret_cast<const float4*>(q + r);
-                    a0 = fmaf(S[r], kk.x, a0);     b0 = fmaf(S[r], qq.x, b0);     c0 = fmaf(kk.x, qq.x, c0);
-                    a1 = fmaf(S[r + 1], kk.y, a1); b1 = fmaf(S[r + 1], qq.y, b1); c0 = fmaf(kk.y, qq.y, c0);
-                    a0 = fmaf(S[r + 2], kk.z, a0); b0 = fmaf(S[r + 2], qq.z, b0); c0 = fmaf(kk.z, qq.z, c0);
-                    a1 = fmaf(S[r + 3], kk.w, a1); b1 = fmaf(S[r + 3], qq.w, b1); c0 = fmaf(kk.w, qq.w, c0);
-                }
-            } else {
-                #pragma unroll
-                for (int r = 0; r < RMAX; r++) {
-                    if (r < R && part * R + r < dk) {
-                        if (r & 1) { a1 = fmaf(S[r], k[r], a1); b1 = fmaf(S[r], q[r], b1); }
-                        else { a0 = fmaf(S[r], k[r], a0); b0 = fmaf(S[r], q[r], b0); }
-                        c0 = fmaf(k[r], q[r], c0);
-                    }
-                }
+            const float* x = sm + buf * per_tile + tt * W;
+            const float4* q4 = reinterpret_cast<const float4*>(x);
+            const float4* k4 = reinterpret_cast<const float4*>(x + LR);
+            const float* tail = x + 2 * LR;
+            const float v = tail[warp * CPW + jj], beta = tail[CB], g = tail[CB + 1], kq = tail[CB + 2];
+            float4 kk[4];
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+            #pragma unroll
+            for (int f = 0; f < 4; f++) {
+                kk[f] = k4[f * L + part];
+                const float4 qq = q4[f * L + part];
+                a0 = fmaf(S[4 * f], kk[f].x, a0);     b0 = fmaf(S[4 * f], qq.x, b0);
+                a1 = fmaf(S[4 * f + 1], kk[f].y, a1); b1 = fmaf(S[4 * f + 1], qq.y, b1);
+                a2 = fmaf(S[4 * f + 2], kk[f].z, a2); b2 = fmaf(S[4 * f + 2], qq.z, b2);
+                a3 = fmaf(S[4 * f + 3], kk[f].w, a3); b3 = fmaf(S[4 * f + 3], qq.w, b3);
             }
-            float* mine = shares + ((tt & 1) * parts + part) * 96;
-            mine[j] = a0 + a1;
-            mine[32 + j] = b0 + b1;
-            mine[64 + j] = c0;
-            __syncthreads();
-            float A = 0.f, B = 0.f, KQ = 0.f;
-            for (int pp = 0; pp < parts; pp++) {
-                const float* x = shares + ((tt & 1) * parts + pp) * 96;
-                A += x[j];
-                B += x[32 + j];
-                KQ += x[64 + j];
+            float A = (a0 + a1) + (a2 + a3), B = (b0 + b1) + (b2 + b3);
+            #pragma unroll
+            for (int o = 1; o < L; o <<= 1) {
+                A += __shfl_xor_sync(0xffffffffu, A, o);
+                B += __shfl_xor_sync(0xffffffffu, B, o);
             }
             const float un = beta * (v - g * A);
-            if (FULL) {
-                #pragma unroll
-                for (int r = 0; r < RMAX; r += 4) {
-                    const float4 kk = *reinterpret_cast<const float4*>(k + r);
-                    S[r] = fmaf(g, S[r], kk.x * un);
-                    S[r + 1] = fmaf(g, S[r + 1], kk.y * un);
-                    S[r + 2] = fmaf(g, S[r + 2], kk.z * un);
-                    S[r + 3] = fmaf(g, S[r + 3], kk.w * un);
-                }
-            } else {
-                #pragma unroll
-                for (int r = 0; r < RMAX; r++)
-                    if (r < R && part * R + r < dk) S[r] = fmaf(g, S[r], k[r] * un);
+            #pragma unroll
+            for (int f = 0; f < 4; f++) {
+                S[4 * f] = fmaf(g, S[4 * f], kk[f].x * un);
+                S[4 * f + 1] = fmaf(g, S[4 * f + 1], kk[f].y * un);
+                S[4 * f + 2] = fmaf(g, S[4 * f + 2], kk[f].z * un);
+                S[4 * f + 3] = fmaf(g, S[4 * f + 3], kk[f].w * un);
             }
-            if (part == 0 && live) out[(size_t)(t0 + tt) * H * dv + h * dv + col] = fmaf(g, B, KQ * un);
+            if (part == 0 && live) out[(size_t)(t0 + tt) * H * dv + h * dv + col] = fmaf(g, B, kq * un);
         }
         ik_cp_async_wait_all();
         __syncthreads();
     }
     if (live) {
         #pragma unroll
-        for (int r = 0; r < RMAX; r++) {
-            const int i = part * R + r;
-            if (r < R && i < dk) st_out[(size_t)i * dv + col] = S[r];
+        for (int r = 0; r < IK_DR_ROWS; r++) {
+            const int i = ((r >> 2) * L + part) * 4 + (r & 3);
+            if (i < dk) st_out[(size_t)i * dv + col] = S[r];
         }
     }
+}
+
+template <int L>
+static cudaError_t ik_delta_rule_launch(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* u, int ldu, int q_off, int k_off,
+                                int v_off, const float* bg, float* state, const int* slots, const int* cu_seqlens, const int* kv_lens,
+                                float* out, int H, int G, int dk, int dv, int TT, int W, int vec) {
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        const cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e != cudaSuccess) return e;
+        raised = true;
+    }
+    return ik_launch(delta_rule_kernel<L>, grid, dim3(threads), smem, stream, u, ldu, q_off, k_off, v_off, bg, state, slots, cu_seqlens,
+                     kv_lens, out, H, G, dk, dv, TT, W, vec);
 }
 
 IK_EXPORT int ik_delta_rule(const float* u, int ldu, int q_off, int k_off, int v_off, const float* bg, float* state, const int* slots,
@@ -194,30 +226,31 @@ IK_EXPORT int ik_delta_rule(const float* u, int ldu, int q_off, int k_off, int v
                             int one_token_each, cudaStream_t stream) {
     if (T < 0 || B < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || !state || !bg) return IK_BAD_ARGUMENT;
     if (T == 0 || B == 0) return IK_OK;
-    if (dk > 512) return IK_UNSUPPORTED;
+    if (dk > 32 * IK_DR_ROWS) return IK_UNSUPPORTED;
     if (one_token_each && T != B) return IK_BAD_ARGUMENT;
-    const int R = dk <= 64 ? 16 : 32;                // rows a thread: two to four warps a block up to 128 rows
-    const int parts = (dk + R - 1) / R;
-    const int W = (2 * dk + 34 + 3) / 4 * 4;
-    const int TT = one_token_each ? 1 : 8;
-    const bool full = dk == parts * R && ldu % 4 == 0;
-    const dim3 grid(B, H, (dv + 31) / 32), block(32, parts);
-    const size_t smem = (size_t)(2 * TT * W + 2 * parts * 96) * sizeof(float);
+    int L = 1;
+    while (L * IK_DR_ROWS < dk) L *= 2;
+    const int cpw = 32 / L;
+    const int nwarps = min(8, (dv + cpw - 1) / cpw), CB = nwarps * cpw, LR = L * IK_DR_ROWS;
+    const int W = (2 * LR + CB + 3 + 3) / 4 * 4;
+    const int TT = one_token_each ? 1 : (W <= 320 ? 16 : 8);
+    const int vec = dk % 4 == 0 && ldu % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && ((uintptr_t)u & 15) == 0;
+    const dim3 grid(B, H, (dv + CB - 1) / CB);
+    const size_t smem = (size_t)(2 * TT * W) * sizeof(float);
     if (smem > 160 * 1024) return IK_UNSUPPORTED;
-#define IK_DR(RMAX, FULL)                                                                                                        \
-    do {                                                                                                                         \
-        static bool raised = false;                                                                                              \
-        if (smem > 48 * 1024 && !raised) {                                                                                       \
-            IK_RETURN_IF_ERROR(cudaFuncSetAttribute(delta_rule_kernel<RMAX, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)); \
-            raised = true;                                                                                                       \
-        }                                                                                                                        \
-        IK_RETURN_IF_ERROR(ik_launch(delta_rule_kernel<RMAX, FULL>, grid, block, smem, stream, u, ldu, q_off, k_off, v_off, bg, state, slots, \
-                                     cu_seqlens, kv_lens, out, H, G, dk, dv, R, TT, W));                                          \
-    } while (0)
-    if (R == 16 && full) IK_DR(16, true);
-    else if (R == 16) IK_DR(16, false);
-    else if (full) IK_DR(32, true);
-    else IK_DR(32, false);
+#define IK_DR(LL)                                                                                                                 \
+    case LL:                                                                                                                      \
+        IK_RETURN_IF_ERROR(ik_delta_rule_launch<LL>(grid, 32 * nwarps, smem, stream, u, ldu, q_off, k_off, v_off, bg, state, slots,   \
+                                                    cu_seqlens, kv_lens, out, H, G, dk, dv, TT, W, vec));                        \
+        break
+    switch (L) {
+        IK_DR(1);
+        IK_DR(2);
+        IK_DR(4);
+        IK_DR(8);
+        IK_DR(16);
+        IK_DR(32);
+    }
 #undef IK_DR
     IK_LAUNCH_STATUS();
 }

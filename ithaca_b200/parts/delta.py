@@ -61,7 +61,7 @@ class GatedDeltaRule:
         if self.n_heads % self.n_qk_heads:
             raise ValueError(f"gated_delta: {self.n_heads} heads cannot share {self.n_qk_heads} query/key heads evenly")
         if self.head_dim > 512:
-            raise ValueError(f"gated_delta: the kernel holds a state column's rows in the registers of up to 16 warps, 32 each; found {self.head_dim}")
+            raise ValueError(f"gated_delta: the kernel holds a state column's rows in the registers of up to 32 lanes, 16 each; found {self.head_dim}")
         if self.taps < 1:
             raise ValueError("gated_delta: the convolution needs at least one tap")
         H, G, dk, dv = self.n_heads, self.n_qk_heads, self.head_dim, self.v_head_dim
