@@ -8,7 +8,8 @@
 // between the lanes of a column per token.
 //
 // The step's tokens are token-major as everywhere: sequence n brings tokens cu_seqlens[n] .. cu_seqlens[n + 1] - 1 at
-// positions kv_lens[n] - count .. kv_lens[n] - 1, its state lies in slot slots[n], kept twice by the parity of the
+// positions kv_lens[n] - count .. kv_lens[n] - 1, its state lies in slot slots[n] as [heads, dv, dk] (the rows of a column
+// side by side), kept twice by the parity of the
 // position it belongs to (a step reads the copy of parity (first - 1) & 1 and writes that of (last) & 1, so a decode
 // step never overwrites what it read and may be run again).  Everything here is float: unit norms, steps, decays
 // (formed in double and rounded once: a decay's error is multiplied into the state at every token), states, sums.
@@ -72,17 +73,16 @@ IK_EXPORT int ik_delta_prepare(float* u, int ldu, int q_off, int k_off, const fl
 // rows in registers (L = 1, 2, .. 32 for up to 16 L rows), the warp therefore holds 32 / L neighbouring columns, and up to
 // eight warps of a block hold neighbouring groups of columns of one head and one sequence.  Lane `part` owns the rows
 // 4 f .. 4 f + 3 of the four groups f = part, L + part, 2 L + part, 3 L + part: the lanes of a column then read
-// consecutive 16-byte words of q and k from shared memory.  Rows beyond dk are staged as zeros and stay zero in the state.
+// consecutive 16-byte words of q and k from shared memory and of the state from memory.  Rows beyond dk are staged as zeros and stay zero in the state.
 //
 // Tokens come through shared memory in tiles of TT (q and k padded to 16 L rows, the block's values of v, the step, the
 // decay and k . q, which a warp forms once per token of a tile for all columns), the next tile on its way (cp.async)
 // while one is computed; there are two block barriers per tile and none per token.  Per token a lane forms its rows' share
 // of A and B in four running sums each, the shares of a column meet by shuffles between neighbouring lanes, and every lane
 // updates its rows.  What is computed for a token depends on its sequence's earlier tokens only, not on where steps or
-// tiles begin, and the sums run in the same order for a prompt and for a single token.
-constexpr int IK_DR_ROWS = 16;
-
-template <int L>
+// tiles begin, and the sums run in the same order for a prompt and for a single token.  The token loop is unrolled by four
+// so that a token's loads and the read-out of the one before overlap with the chain S -> A -> u -> S.
+template <int L, int R>
 __global__ void __launch_bounds__(256)
 delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, int v_off, const float* __restrict__ bg,
                   float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu_seqlens,
@@ -95,7 +95,7 @@ delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
     IK_AFTER_WAIT(cu_seqlens);
     IK_AFTER_WAIT(kv_lens);
     ik_pdl_launch_dependents();
-    constexpr int LR = L * IK_DR_ROWS, CPW = 32 / L;
+    constexpr int LR = L * R, CPW = 32 / L, NF = R / 4;
     const int b = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, nthreads = blockDim.x, warp = tid >> 5, lane = tid & 31;
     const int nwarps = nthreads >> 5, CB = nwarps * CPW;
     const int part = lane % L, jj = lane / L;
@@ -107,36 +107,36 @@ delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
     if (hi <= lo) return;
     const int kvh = h / (H / G);
     const size_t per = (size_t)H * dk * dv;
-    const float* st_in = state + ((size_t)slots[b] * 2 + ((start - 1) & 1)) * per + (size_t)h * dk * dv;
-    float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * per + (size_t)h * dk * dv;
-    float S[IK_DR_ROWS];
+    const float* st_in = state + ((size_t)slots[b] * 2 + ((start - 1) & 1)) * per + ((size_t)h * dv + ccol) * dk;
+    float* st_out = state + ((size_t)slots[b] * 2 + ((end - 1) & 1)) * per + ((size_t)h * dv + ccol) * dk;
+    float S[R];
     #pragma unroll
-    for (int r = 0; r < IK_DR_ROWS; r++) {
+    for (int r = 0; r < R; r++) {
         const int i = ((r >> 2) * L + part) * 4 + (r & 3);
-        S[r] = (i < dk && start > 0) ? st_in[(size_t)i * dv + ccol] : 0.f;
+        S[r] = (i < dk && start > 0) ? st_in[i] : 0.f;
     }
-    auto stage = [&](int t0, int buf) {
+    auto stage = [&](int t0, int buf) {                  // a warp brings whole tokens: every warp does the same share
         const int n = min(TT, hi - t0);
-        for (int tt = 0; tt < n; tt++) {
+        for (int tt = warp; tt < n; tt += nwarps) {
             const float* row = u + (size_t)(t0 + tt) * ldu;
             float* dst = sm + buf * per_tile + tt * W;
             const float* qs = row + q_off + kvh * dk;
             const float* ks = row + k_off + kvh * dk;
             if (vec) {                                   // dk a multiple of 4 and every row of q and k on a 16-byte boundary
-                for (int f = tid; f < 2 * (LR / 4); f += nthreads) {
+                for (int f = lane; f < 2 * (LR / 4); f += 32) {
                     const int g4 = f < LR / 4 ? f : f - LR / 4;
                     const float* src = (f < LR / 4 ? qs : ks) + 4 * g4;
                     if (4 * g4 < dk) ik_cp_async16(dst + 4 * f, src);
                     else *reinterpret_cast<float4*>(dst + 4 * f) = make_float4(0.f, 0.f, 0.f, 0.f);
                 }
             } else {
-                for (int w = tid; w < 2 * LR; w += nthreads) {
+                for (int w = lane; w < 2 * LR; w += 32) {
                     const int i = w < LR ? w : w - LR;
                     if (i < dk) ik_cp_async4(dst + w, (w < LR ? qs : ks) + i);
                     else dst[w] = 0.f;
                 }
             }
-            for (int w = tid; w < CB + 2; w += nthreads) {
+            for (int w = lane; w < CB + 2; w += 32) {
                 if (w < CB) {
                     if (col0 + w < dv) ik_cp_async4(dst + 2 * LR + w, row + v_off + h * dv + col0 + w);
                     else dst[2 * LR + w] = 0.f;
@@ -162,16 +162,17 @@ delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
             if (lane == 0) x[2 * LR + CB + 2] = c;
         }
         __syncthreads();
+        #pragma unroll 4
         for (int tt = 0; tt < n_here; tt++) {
             const float* x = sm + buf * per_tile + tt * W;
             const float4* q4 = reinterpret_cast<const float4*>(x);
             const float4* k4 = reinterpret_cast<const float4*>(x + LR);
             const float* tail = x + 2 * LR;
             const float v = tail[warp * CPW + jj], beta = tail[CB], g = tail[CB + 1], kq = tail[CB + 2];
-            float4 kk[4];
+            float4 kk[NF];
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
             #pragma unroll
-            for (int f = 0; f < 4; f++) {
+            for (int f = 0; f < NF; f++) {
                 kk[f] = k4[f * L + part];
                 const float4 qq = q4[f * L + part];
                 a0 = fmaf(S[4 * f], kk[f].x, a0);     b0 = fmaf(S[4 * f], qq.x, b0);
@@ -187,7 +188,7 @@ delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
             }
             const float un = beta * (v - g * A);
             #pragma unroll
-            for (int f = 0; f < 4; f++) {
+            for (int f = 0; f < NF; f++) {
                 S[4 * f] = fmaf(g, S[4 * f], kk[f].x * un);
                 S[4 * f + 1] = fmaf(g, S[4 * f + 1], kk[f].y * un);
                 S[4 * f + 2] = fmaf(g, S[4 * f + 2], kk[f].z * un);
@@ -200,24 +201,24 @@ delta_rule_kernel(const float* __restrict__ u, int ldu, int q_off, int k_off, in
     }
     if (live) {
         #pragma unroll
-        for (int r = 0; r < IK_DR_ROWS; r++) {
+        for (int r = 0; r < R; r++) {
             const int i = ((r >> 2) * L + part) * 4 + (r & 3);
-            if (i < dk) st_out[(size_t)i * dv + col] = S[r];
+            if (i < dk) st_out[i] = S[r];
         }
     }
 }
 
-template <int L>
+template <int L, int R>
 static cudaError_t ik_delta_rule_launch(dim3 grid, int threads, size_t smem, cudaStream_t stream, const float* u, int ldu, int q_off, int k_off,
-                                int v_off, const float* bg, float* state, const int* slots, const int* cu_seqlens, const int* kv_lens,
-                                float* out, int H, int G, int dk, int dv, int TT, int W, int vec) {
+                                        int v_off, const float* bg, float* state, const int* slots, const int* cu_seqlens,
+                                        const int* kv_lens, float* out, int H, int G, int dk, int dv, int TT, int W, int vec) {
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
-        const cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<L>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        const cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<L, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         if (e != cudaSuccess) return e;
         raised = true;
     }
-    return ik_launch(delta_rule_kernel<L>, grid, dim3(threads), smem, stream, u, ldu, q_off, k_off, v_off, bg, state, slots, cu_seqlens,
+    return ik_launch(delta_rule_kernel<L, R>, grid, dim3(threads), smem, stream, u, ldu, q_off, k_off, v_off, bg, state, slots, cu_seqlens,
                      kv_lens, out, H, G, dk, dv, TT, W, vec);
 }
 
@@ -226,12 +227,13 @@ IK_EXPORT int ik_delta_rule(const float* u, int ldu, int q_off, int k_off, int v
                             int one_token_each, cudaStream_t stream) {
     if (T < 0 || B < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || !state || !bg) return IK_BAD_ARGUMENT;
     if (T == 0 || B == 0) return IK_OK;
-    if (dk > 32 * IK_DR_ROWS) return IK_UNSUPPORTED;
+    if (dk > 32 * 16) return IK_UNSUPPORTED;         // 32 lanes of 16 rows
     if (one_token_each && T != B) return IK_BAD_ARGUMENT;
+    constexpr int R = 16;                            // rows a lane keeps
     int L = 1;
-    while (L * IK_DR_ROWS < dk) L *= 2;
+    while (L * R < dk) L *= 2;
     const int cpw = 32 / L;
-    const int nwarps = min(8, (dv + cpw - 1) / cpw), CB = nwarps * cpw, LR = L * IK_DR_ROWS;
+    const int nwarps = min(8, (dv + cpw - 1) / cpw), CB = nwarps * cpw, LR = L * R;
     const int W = (2 * LR + CB + 3 + 3) / 4 * 4;
     const int TT = one_token_each ? 1 : (W <= 320 ? 16 : 8);
     const int vec = dk % 4 == 0 && ldu % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && ((uintptr_t)u & 15) == 0;
@@ -240,8 +242,8 @@ IK_EXPORT int ik_delta_rule(const float* u, int ldu, int q_off, int k_off, int v
     if (smem > 160 * 1024) return IK_UNSUPPORTED;
 #define IK_DR(LL)                                                                                                                 \
     case LL:                                                                                                                      \
-        IK_RETURN_IF_ERROR(ik_delta_rule_launch<LL>(grid, 32 * nwarps, smem, stream, u, ldu, q_off, k_off, v_off, bg, state, slots,   \
-                                                    cu_seqlens, kv_lens, out, H, G, dk, dv, TT, W, vec));                        \
+        IK_RETURN_IF_ERROR(ik_delta_rule_launch<LL, R>(grid, 32 * nwarps, smem, stream, u, ldu, q_off, k_off, v_off, bg, state, slots, \
+                                                       cu_seqlens, kv_lens, out, H, G, dk, dv, TT, W, vec));                     \
         break
     switch (L) {
         IK_DR(1);

@@ -1068,7 +1068,7 @@ def decay_attention(p: torch.Tensor, q_off: int, k_off: int, v_off: int, decay: 
                     n_heads: int, dk: int, dv: int, act: int = 1) -> torch.Tensor:
     """Linear attention with one constant decay per head: S <- a S + k v^T, o = S^T q, over the step's tokens.  q, k, v
     are column ranges of ``p`` (float), passed through silu when ``act`` (2: silu with the hardware's approximate
-    exponential and reciprocal, for the 16-bit path).  ``state`` [max_slots, 2, heads, dk, dv] float.
+    exponential and reciprocal, for the 16-bit path).  ``state`` [max_slots, 2, heads, dv, dk] float (column by column).
     Returns float [T, heads * dv]."""
     _need(p, "p", torch.float32, contiguous=False)
     _need(decay, "decay", torch.float32)
@@ -1244,12 +1244,12 @@ def delta_rule(u: torch.Tensor, q_off: int, k_off: int, v_off: int, bg: torch.Te
                n_qk_heads: int, dk: int, dv: int) -> torch.Tensor:
     """The gated delta rule over the step's tokens: per head S <- g S; u = b (v - S^T k); S <- S + k u^T; o = S^T q.  q, k
     (``n_qk_heads`` heads, unit vectors) and v are column ranges of ``u`` (float), ``bg`` [T, 2, heads] the steps and decays,
-    ``state`` [max_slots, 2, heads, dk, dv] float.  Returns float [T, heads * dv]."""
+    ``state`` [max_slots, 2, heads, dv, dk] float (column by column).  Returns float [T, heads * dv]."""
     _need(u, "u", torch.float32)
     _need(bg, "bg", torch.float32)
     _need(state, "state", torch.float32)
     T = u.shape[0]
-    if tuple(state.shape[1:]) != (2, n_heads, dk, dv) or bg.shape != (T, 2, n_heads) or n_heads % n_qk_heads \
+    if tuple(state.shape[1:]) != (2, n_heads, dv, dk) or bg.shape != (T, 2, n_heads) or n_heads % n_qk_heads \
             or max(q_off + n_qk_heads * dk, k_off + n_qk_heads * dk, v_off + n_heads * dv) > u.shape[1]:
         raise KernelError("delta_rule: the sizes do not fit together")
     out = torch.empty((T, n_heads * dv), dtype=torch.float32, device=u.device)

@@ -13,7 +13,8 @@ sequence's first token:
 so the read-out sees the current token's write.  Every head's o is RMS-normed over its values (``norm_eps`` inside the
 root) with one weight of size v_head_dim that the heads share, multiplied by silu(Wg x), and projected out.
 
-Per sequence and cache entry the mixer keeps S as float32 [2, heads, head_dim, v_head_dim] (two copies by the parity of
+Per sequence and cache entry the mixer keeps S as float32 [2, heads, v_head_dim, head_dim], a column's rows side by side
+(a column is a recurrence of its own and the kernel gives it to a few lanes; two copies by the parity of
 the position the state belongs to, so that a decode step never overwrites what it read and may be run twice) and a ring
 of the last ``conv_taps`` inputs of the convolution, float32.  One product gives [q | k | v | g | b | a] in float; the
 convolution's result, the unit norms, steps, decays, the state and its sums are float32 on both paths; only the
@@ -82,7 +83,7 @@ class GatedDeltaRule:
         self.runtime = runtime
 
     def cache_requests(self) -> List[object]:
-        out: List[object] = [StateRequest(STATE, (2, self.n_heads, self.head_dim, self.v_head_dim), "float32")]
+        out: List[object] = [StateRequest(STATE, (2, self.n_heads, self.v_head_dim, self.head_dim), "float32")]
         if self.taps > 1:
             out.append(StateRequest(RING, (self.taps, self.channels), "float32"))
         return out

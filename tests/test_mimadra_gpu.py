@@ -369,7 +369,7 @@ def test_gated_delta_rule_kernels(H, G, dk, dv, taps):
     p = [torch.randn(l, pad + C + 2 * H, generator=g) for l in TOTAL]
     cw = torch.randn(C, taps, generator=g) * 0.6
     A_log, dt_bias = torch.randn(H, generator=g) * 0.5 - 0.5, torch.randn(H, generator=g) * 0.5 - 1.0
-    state = torch.full((6, 2, H, dk, dv), 7.0, device=DEV)
+    state = torch.full((6, 2, H, dv, dk), 7.0, device=DEV)
     ring = torch.full((6, taps, C), 9.0, device=DEV) if taps > 1 else None
     got = [[] for _ in TOTAL]
     for lo, hi in STEPS:
