@@ -73,7 +73,8 @@ IK_EXPORT int ik_delta_prepare(float* u, int ldu, int q_off, int k_off, const fl
 // rows in registers (L = 1, 2, .. 32 for up to 16 L rows), the warp therefore holds 32 / L neighbouring columns, and up to
 // eight warps of a block hold neighbouring groups of columns of one head and one sequence.  Lane `part` owns the rows
 // 4 f .. 4 f + 3 of the four groups f = part, L + part, 2 L + part, 3 L + part: the lanes of a column then read
-// consecutive 16-byte words of q and k from shared memory and of the state from memory.  Rows beyond dk are staged as zeros and stay zero in the state.
+// consecutive 16-byte words of q and k from shared memory and of the state from memory.  Rows beyond dk are staged as
+// zeros and stay zero in the state.
 //
 // Tokens come through shared memory in tiles of TT (q and k padded to 16 L rows, the block's values of v, the step, the
 // decay and k . q, which a warp forms once per token of a tile for all columns), the next tile on its way (cp.async)
