@@ -12,6 +12,7 @@ from dataclasses import dataclass
 from typing import Any, Callable, Dict, Optional
 
 from .base import ConfigError, load_config_dict
+from .gunenex import GunenexConfig
 from .llama import LlamaConfig
 from .mimadra import MimadraConfig
 from .tiralix import TiralixConfig
@@ -69,3 +70,4 @@ register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
 register_architecture(VebisunConfig.ARCHITECTURE, VebisunConfig)
 register_architecture(TiralixConfig.ARCHITECTURE, TiralixConfig)
 register_architecture(MimadraConfig.ARCHITECTURE, MimadraConfig)
+register_architecture(GunenexConfig.ARCHITECTURE, GunenexConfig)

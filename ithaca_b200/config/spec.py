@@ -78,6 +78,10 @@ class ModelSpec:
     # tensors a folder may hold although the model does not ask for them, because they repeat another one:
     # name -> the tensor it must equal (a tied output matrix stored beside the embedding, for instance)
     aliases: Dict[str, str] = field(default_factory=dict)
+    # residual streams per token: 0 = the plain single stream [T, d].  With n >= 1 the stream tensor is [T, n, d]: the
+    # embedding's output is copied into each, the blocks (kind ``hyper``) read and write all of them, and the final norm
+    # reads their sum
+    streams: int = 0
 
     def n_cache_entries(self) -> int:
         return 1 + max((e.cache for e in self.schedule), default=-1)

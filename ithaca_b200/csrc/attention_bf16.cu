@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(32 * NW)
 attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                     bf16* __restrict__ out, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
                     const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, float cap_log2e, int window,
-                    int sink, int n_pages, int* status) {
+                    int sink, const float* __restrict__ sink_v, int n_pages, int* status) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
     constexpr int BM = 16 * NW, THREADS = 32 * NW, CH = HD / 8;          // CH: 16-byte chunks per row
@@ -133,7 +133,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages
         for (int e = 0; e < 4; e++) o[d][e] = 0.f;
     // a sink is one more key of score 0 without a value: the running maximum starts at 0 and the sum at 1 (the sum is
     // kept in four parts by the threads of a row; thread 0 of the four has the sink's)
-    float m_i[2] = {sink ? 0.f : -INFINITY, sink ? 0.f : -INFINITY}, l_i[2] = {(sink && t == 0) ? 1.f : 0.f, (sink && t == 0) ? 1.f : 0.f};
+    // (with sink_v the sink's score is the head's own number instead of 0, here in the exponent's base-2 units)
+    const float m_sink = sink ? (sink_v ? sink_v[h] * 1.4426950408889634f : 0.f) : -INFINITY;
+    float m_i[2] = {m_sink, m_sink}, l_i[2] = {(sink && t == 0) ? 1.f : 0.f, (sink && t == 0) ? 1.f : 0.f};
     const int my_pos[2] = {pos_lo + warp * 16 + g, pos_lo + warp * 16 + g + 8};
     const bool my_row[2] = {warp * 16 + g < rows, warp * 16 + g + 8 < rows};
 
@@ -270,7 +272,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,
                        const int* __restrict__ table, int table_stride, int nh, int nkv, float scale_log2e, float cap_log2e,
-                       int window, int sink, int n_pages, int* status) {
+                       int window, int sink, const float* __restrict__ sink_v, int n_pages, int* status) {
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     ik_pdl_wait();
     ik_pdl_launch_dependents();
@@ -406,7 +408,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool row_valid = r < rows;
         const int pos_r = pos_lo + r;
-        float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;      // a sink: one more key of score 0 without a value
+        // a sink: one more key without a value, of score 0 or (sink_v) of the head's own score, in base-2 units
+        float m = sink ? (sink_v ? sink_v[h] * 1.4426950408889634f : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;
         bool ok = true;
         for (int i = 0; i < n_iter && ok; i++) {
             const int p = p_lo + i;
@@ -718,7 +721,7 @@ attn_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
 // Merges the partials of each (sequence, head) in chunk order and writes the normalised output.
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     bf16* __restrict__ out, const int* __restrict__ kv_lens, int nh, int window,
-                                    int sink, int chunk_pages, int n_splits) {
+                                    int sink, const float* __restrict__ sink_v, int chunk_pages, int n_splits) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
     const int b = blockIdx.x, h = blockIdx.y;
@@ -726,11 +729,13 @@ __global__ void attn_combine_kernel(const float* __restrict__ part_o, const floa
     const int j0 = (window > 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int s_first = (j0 / PAGE) / chunk_pages, s_last = (pos / PAGE) / chunk_pages;
     const size_t base = ((size_t)b * nh + h) * n_splits;
-    float mm = sink ? 0.f : -INFINITY;                             // a sink joins the merge as one more part: score 0, sum 1, no values
+    // a sink joins the merge as one more part: score 0 (or the head's own, in base-2 units), sum 1, no values
+    const float m_sink = sink ? (sink_v ? sink_v[h] * 1.4426950408889634f : 0.f) : -INFINITY;
+    float mm = m_sink;
     for (int s = s_first; s <= s_last; s++) mm = fmaxf(mm, part_ml[(base + s) * 2]);
     const float m_use = mm == -INFINITY ? 0.f : mm;
     for (int x = threadIdx.x; x < HD; x += blockDim.x) {
-        float acc = 0.f, ll = sink ? exp2f(-m_use) : 0.f;
+        float acc = 0.f, ll = sink ? exp2f(m_sink - m_use) : 0.f;
         for (int s = s_first; s <= s_last; s++) {
             const float a = exp2f(part_ml[(base + s) * 2] - m_use);
             acc += part_o[(base + s) * HD + x] * a;
@@ -751,7 +756,7 @@ IK_EXPORT int ik_attn_take_wait_record(int* out4) { return ik_take_wait_record(o
 
 IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
                               const int* kv_lens, const int* table, int table_stride, int B, int max_new, int nh,
-                              int nkv, float scale, float softcap, int window, int sink, int page_size, int n_pages, int* status,
+                              int nkv, float scale, float softcap, int window, int sink, const float* sink_v, int page_size, int n_pages, int* status,
                               cudaStream_t stream) {
     const float sc_a = softcap > 0.f ? scale / softcap : scale * 1.4426950408889634f, sc_b = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     if (B <= 0 || max_new <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || B > 65535 || nh > 65535)
@@ -766,14 +771,14 @@ IK_EXPORT int ik_attn_prefill(const void* q, const void* k_pages, const void* v_
     dim3 grid((max_new + BM - 1) / BM, nh, B);
     IK_RETURN_IF_ERROR(ik_launch(kern, grid, 32 * NW, smem, stream, (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out,
                                           cu_seqlens, kv_lens, table, table_stride, nh, nkv,
-                                          sc_a, sc_b, window, sink, n_pages, status));
+                                          sc_a, sc_b, window, sink, sink_v, n_pages, status));
     IK_LAUNCH_STATUS();
 }
 
 // The tcgen05 kernel (head sizes 64 and 128; IK_UNSUPPORTED otherwise).  T: rows of q.
 IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void* v_pages, void* out, const int* cu_seqlens,
                                  const int* kv_lens, const int* table, int table_stride, int T, int B, int max_new, int nh,
-                                 int nkv, float scale, float softcap, int window, int sink, int page_size, int n_pages, int* status,
+                                 int nkv, float scale, float softcap, int window, int sink, const float* sink_v, int page_size, int n_pages, int* status,
                                  cudaStream_t stream) {
 #if IK_HD == 64 || IK_HD == 128
     const float sc_a = softcap > 0.f ? scale / softcap : scale * 1.4426950408889634f, sc_b = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
@@ -794,7 +799,7 @@ IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void*
     if (e != cudaSuccess) return (int)e;
     dim3 grid((max_new + TC_BM - 1) / TC_BM, nh, B);
     IK_RETURN_IF_ERROR(ik_launch(kern, grid, 192, TC_SMEM, stream, mq, mk, mv, (bf16*)out, cu_seqlens, kv_lens, table,
-                                 table_stride, nh, nkv, sc_a, sc_b, window, sink, n_pages, status));
+                                 table_stride, nh, nkv, sc_a, sc_b, window, sink, sink_v, n_pages, status));
     IK_LAUNCH_STATUS();
 #else
     return IK_UNSUPPORTED;
@@ -805,7 +810,7 @@ IK_EXPORT int ik_attn_prefill_tc(const void* q, const void* k_pages, const void*
 // n_splits must cover the longest sequence: n_splits * chunk_pages * 64 >= max kv length.
 IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_pages, void* out, float* part_o,
                              float* part_ml, const int* kv_lens, const int* table, int table_stride, int B, int nh,
-                             int nkv, float scale, float softcap, int window, int sink, int page_size, int n_pages, int chunk_pages,
+                             int nkv, float scale, float softcap, int window, int sink, const float* sink_v, int page_size, int n_pages, int chunk_pages,
                              int n_splits, int ring_kb, int* status, cudaStream_t stream) {
     const float sc_a = softcap > 0.f ? scale / softcap : scale * 1.4426950408889634f, sc_b = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     if (B <= 0 || nh <= 0 || nkv <= 0 || nh % nkv || page_size != PAGE || chunk_pages <= 0 || n_splits <= 0 ||
@@ -837,6 +842,6 @@ IK_EXPORT int ik_attn_decode(const void* q, const void* k_pages, const void* v_p
     if (e != cudaSuccess) return (int)e;
     dim3 grid2(B, nh);
     IK_RETURN_IF_ERROR(ik_launch_family(IK_FAMILY_ATTENTION_MERGE, attn_combine_kernel, grid2, HD < 128 ? HD : 128, 0, stream, part_o, part_ml, (bf16*)out, kv_lens, nh, window,
-                                                                    sink, chunk_pages, n_splits));
+                                                                    sink, sink_v, chunk_pages, n_splits));
     IK_LAUNCH_STATUS();
 }

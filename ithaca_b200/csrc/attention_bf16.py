@@ -51,11 +51,11 @@ def module(head_dim: int) -> ctypes.CDLL:
     m = _modules.get(key)
     if m is None:
         m = build.load_library(f"ithaca_attn_hd{head_dim}", ["attention_bf16.cu"], defines=[f"IK_HD={head_dim}"])
-        m.ik_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _vp, _vp]
+        m.ik_attn_prefill.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _i, _i, _vp, _vp]
         m.ik_attn_prefill.restype = _i
-        m.ik_attn_prefill_tc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _vp, _vp]
+        m.ik_attn_prefill_tc.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _i, _i, _vp, _vp]
         m.ik_attn_prefill_tc.restype = _i
-        m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _i, _i, _i,
+        m.ik_attn_decode.argtypes = [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _i, _i, _i, _i, _i,
                                      _vp, _vp]
         m.ik_attn_decode.restype = _i
         m.ik_attn_take_wait_record.argtypes = [_vp]
@@ -69,10 +69,11 @@ def module(head_dim: int) -> ctypes.CDLL:
 def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_seqlens: torch.Tensor,
             kv_lens: torch.Tensor, table: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, scale: float,
             window: int, status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
-            kind: str = "auto", work: Optional[Tuple[int, int]] = None, softcap: float = 0.0, sink: bool = False) -> torch.Tensor:
+            kind: str = "auto", work: Optional[Tuple[int, int]] = None, softcap: float = 0.0, sink=False) -> torch.Tensor:
     """``kind``: "tc" = the tcgen05 kernel (head sizes 64 and 128), "mma" = the warp-level kernel,
     "auto" = tcgen05 where it applies.  ``softcap``: scores become cap * tanh(score / cap) (0 = no cap).  ``sink``: the
-    softmax's denominator counts one more key of score 0 that carries no value."""
+    softmax's denominator counts one more key of score 0 that carries no value (True), or of a score per head (a float32
+    tensor [n_heads], not scaled)."""
     n_pages, nkv, page_size, hd = k_pages.shape
     m = module(hd)
     if out is None:
@@ -81,7 +82,7 @@ def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_se
         ops._work(f"attention prefill tcgen05 {q.shape[0]}x{n_heads}", *(work or (0, 0)))
         st = m.ik_attn_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
                                   _ptr(table), table.stride(0), q.shape[0], n_seqs, max_new, n_heads, nkv, scale, softcap, window,
-                                  1 if sink else 0, page_size, n_pages, _ptr(status), _stream())
+                                  ops.sink_flag(sink), _ptr(ops.sink_values(sink, n_heads)), page_size, n_pages, _ptr(status), _stream())
         if st != -2:
             _check(st, "attention prefill (tcgen05)")
             return out
@@ -89,15 +90,15 @@ def prefill(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, cu_se
             raise KernelError("attention prefill (tcgen05): head size or alignment not supported")
     ops._work(f"attention prefill mma {q.shape[0]}x{n_heads}", *(work or (0, 0)))
     _check(m.ik_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
-                             _ptr(table), table.stride(0), n_seqs, max_new, n_heads, nkv, scale, softcap, window, 1 if sink else 0,
-                             page_size, n_pages, _ptr(status), _stream()), "attention prefill")
+                             _ptr(table), table.stride(0), n_seqs, max_new, n_heads, nkv, scale, softcap, window, ops.sink_flag(sink),
+                             _ptr(ops.sink_values(sink, n_heads)), page_size, n_pages, _ptr(status), _stream()), "attention prefill")
     return out
 
 
 def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_lens: torch.Tensor, table: torch.Tensor,
            n_seqs: int, kv_len_bound: int, n_heads: int, scale: float, window: int, status: Optional[torch.Tensor],
            out: Optional[torch.Tensor] = None, chunk_pages: int = DECODE_CHUNK_PAGES, ring_kb: int = 0,
-           work: Optional[Tuple[int, int]] = None, softcap: float = 0.0, sink: bool = False) -> torch.Tensor:
+           work: Optional[Tuple[int, int]] = None, softcap: float = 0.0, sink=False) -> torch.Tensor:
     """``kv_len_bound``: no sequence of the step is longer than this (it sizes the grid and the
     scratch for the partial results; blocks beyond a sequence's length return at once)."""
     n_pages, nkv, page_size, hd = k_pages.shape
@@ -110,12 +111,13 @@ def decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, kv_len
     ops._work(f"attention decode {n_seqs}x{n_heads}", *(work or (0, 0)))
     _check(m.ik_attn_decode(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(out), _ptr(part_o), _ptr(part_ml),
                             _ptr(kv_lens), _ptr(table), table.stride(0), n_seqs, n_heads, nkv, scale, softcap, window,
-                            1 if sink else 0, page_size, n_pages, chunk_pages, n_splits, ring_kb, _ptr(status), _stream()), "attention decode", kernels=2)
+                            ops.sink_flag(sink), _ptr(ops.sink_values(sink, n_heads)), page_size, n_pages, chunk_pages, n_splits, ring_kb,
+                            _ptr(status), _stream()), "attention decode", kernels=2)
     return out
 
 
 def attend(q, k_pages, v_pages, ctx, table, n_heads: int, scale: float, window: int,
-           status, softcap: float = 0.0, sink: bool = False) -> Optional[torch.Tensor]:
+           status, softcap: float = 0.0, sink=False) -> Optional[torch.Tensor]:
     """Returns None when no specialised kernel takes these sizes or options (the caller then uses the
     CUDA-core kernel)."""
     n_pages, nkv, page_size, hd = k_pages.shape

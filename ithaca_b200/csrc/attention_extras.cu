@@ -11,6 +11,8 @@
 // pairing 0 turns (i, i + rot/2), pairing 1 turns (2i, 2i + 1), by float(pos) * inv_freq[i]; cos and sin are multiplied
 // by `magnitude`.  q goes to q_out [T, nh*hd]; k and v into the token's place in the pages
 // (pages[page][kv head][position in page][size], page = table[seq * table_stride + pos / page_size]).
+// `bias` (or null) is a vector over p's columns that is added to q, k and v as they are read.  With v_norm every value head
+// is divided by the root mean square of its own hdv values (eps inside the root, no weight) before it is stored.
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(256)
 norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_off, int v_off, const float* __restrict__ q_w,
@@ -18,8 +20,8 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
                         TC* __restrict__ v_pages, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                         const int* __restrict__ table, int table_stride, const float* __restrict__ inv_freq, float magnitude,
                         int nh, int nkv, int hd, int hdv, int rot, int pairing, int page_size, int n_pages, int write_cache,
-                        int per_head, int* status) {
-    extern __shared__ __align__(16) float cs[];          // [rot/2] cos, [rot/2] sin, then per_head: [nh + nkv] 1 / rms
+                        int per_head, const float* __restrict__ bias, int v_norm, int* status) {
+    extern __shared__ __align__(16) float cs[];          // [rot/2] cos, [rot/2] sin, [nh + nkv] 1 / rms (per_head), [nkv] 1 / rms of v
     __shared__ float red[32];
     ik_pdl_wait();
     IK_AFTER_WAIT(p);
@@ -36,14 +38,28 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
     }
     float rq = 1.f, rk = 1.f;
     float* head_r = cs + rot;
+    float* v_r = head_r + (per_head ? nh + nkv : 0);
+    if (v_norm) {
+        for (int head = threadIdx.x >> 5; head < nkv; head += 8) {
+            const float* src = row + v_off + head * hdv;
+            const float* b = bias ? bias + v_off + head * hdv : nullptr;
+            float ss = 0.f;
+            for (int i = threadIdx.x & 31; i < hdv; i += 32) { const float v = b ? src[i] + b[i] : src[i]; ss = fmaf(v, v, ss); }
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if ((threadIdx.x & 31) == 0) v_r[head] = 1.0f / sqrtf(ss / (float)hdv + eps);
+        }
+    }
     if (per_head) {
         // one warp per head, lanes in index order, then the shuffle tree: the sum's order depends on hd alone
         for (int head = threadIdx.x >> 5; head < nh + nkv; head += 8) {
             const bool is_q = head < nh;
-            const float* src = is_q ? row + q_off + head * hd : row + k_off + (head - nh) * hd;
+            const int col = is_q ? q_off + head * hd : k_off + (head - nh) * hd;
+            const float* src = row + col;
+            const float* b = bias ? bias + col : nullptr;
             float ss = 0.f;
             if (is_q ? q_w != nullptr : k_w != nullptr) {
-                for (int i = threadIdx.x & 31; i < hd; i += 32) { const float v = src[i]; ss = fmaf(v, v, ss); }
+                for (int i = threadIdx.x & 31; i < hd; i += 32) { const float v = b ? src[i] + b[i] : src[i]; ss = fmaf(v, v, ss); }
                 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             }
@@ -51,13 +67,13 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
         }
     } else if (q_w) {
         float ss = 0.f;
-        for (int i = threadIdx.x; i < nh * hd; i += 256) { const float v = row[q_off + i]; ss = fmaf(v, v, ss); }
+        for (int i = threadIdx.x; i < nh * hd; i += 256) { const float v = row[q_off + i] + (bias ? bias[q_off + i] : 0.f); ss = fmaf(v, v, ss); }
         ss = ik_block_sum<256>(ss, red);
         rq = 1.0f / sqrtf(ss / (float)(nh * hd) + eps);
     }
     if (k_w && !per_head) {
         float ss = 0.f;
-        for (int i = threadIdx.x; i < nkv * hd; i += 256) { const float v = row[k_off + i]; ss = fmaf(v, v, ss); }
+        for (int i = threadIdx.x; i < nkv * hd; i += 256) { const float v = row[k_off + i] + (bias ? bias[k_off + i] : 0.f); ss = fmaf(v, v, ss); }
         ss = ik_block_sum<256>(ss, red);
         rk = 1.0f / sqrtf(ss / (float)(nkv * hd) + eps);
     }
@@ -75,16 +91,20 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
         const int head = e / hd, i = e - head * hd;
         const bool is_q = head < nh;
         if (!is_q && !page_ok) continue;
-        const float* src = is_q ? row + q_off + head * hd : row + k_off + (head - nh) * hd;
+        const int col = is_q ? q_off + head * hd : k_off + (head - nh) * hd;
+        const float* src = row + col;
+        const float* b = bias ? bias + col : nullptr;
         const float* w = is_q ? (q_w ? q_w + (per_head ? 0 : head * hd) : nullptr) : (k_w ? k_w + (per_head ? 0 : (head - nh) * hd) : nullptr);
         const float r = per_head ? head_r[head] : is_q ? rq : rk;
-        float val = w ? src[i] * r * w[i] : src[i];
+        const float mine = b ? src[i] + b[i] : src[i];
+        float val = w ? mine * r * w[i] : mine;
         if (i < rot) {
             int partner, f;
             bool first;
             if (pairing == 0) { first = i < half; partner = first ? i + half : i - half; f = first ? i : i - half; }
             else { first = (i & 1) == 0; partner = first ? i + 1 : i - 1; f = i >> 1; }
-            const float other = w ? src[partner] * r * w[partner] : src[partner];
+            const float theirs = b ? src[partner] + b[partner] : src[partner];
+            const float other = w ? theirs * r * w[partner] : theirs;
             const float c = cs[f], s = cs[half + f];
             // (u, v) -> (u c - v s, v c + u s); `first` holds u
             val = first ? __fsub_rn(__fmul_rn(val, c), __fmul_rn(other, s)) : __fadd_rn(__fmul_rn(val, c), __fmul_rn(other, s));
@@ -95,7 +115,10 @@ norm_rope_append_kernel(const float* __restrict__ p, int ldp, int q_off, int k_o
     if (page_ok) {
         for (int e = threadIdx.x; e < nkv * hdv; e += 256) {
             const int head = e / hdv, i = e - head * hdv;
-            ik_st(v_pages, (page_off + (size_t)head * page_size) * hdv + i, row[v_off + e]);
+            float val = row[v_off + e];
+            if (bias) val += bias[v_off + e];
+            if (v_norm) val *= v_r[head];
+            ik_st(v_pages, (page_off + (size_t)head * page_size) * hdv + i, val);
         }
     }
 }
@@ -104,16 +127,17 @@ IK_EXPORT int ik_norm_rope_append(const float* p, int ldp, int q_off, int k_off,
                                   float eps, void* q_out, int q_dtype, void* k_pages, void* v_pages, int cache_dtype,
                                   const int* token_seq, const int* token_pos, const int* table, int table_stride,
                                   const float* inv_freq, float magnitude, int T, int nh, int nkv, int hd, int hdv, int rot,
-                                  int pairing, int page_size, int n_pages, int write_cache, int per_head, int* status, cudaStream_t stream) {
+                                  int pairing, int page_size, int n_pages, int write_cache, int per_head, const float* bias, int v_norm, int* status,
+                                  cudaStream_t stream) {
     if (T < 0 || nh <= 0 || nkv <= 0 || hd <= 0 || hdv <= 0 || rot < 0 || rot > hd || (rot & 1) || page_size <= 0)
         return IK_BAD_ARGUMENT;
     if (rot > 0 && !inv_freq) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
-    const size_t smem = (size_t)(rot + (per_head ? nh + nkv : 0)) * sizeof(float);
+    const size_t smem = (size_t)(rot + (per_head ? nh + nkv : 0) + (v_norm ? nkv : 0)) * sizeof(float);
 #define IK_NRA(TQ, TC)                                                                                                       \
     IK_RETURN_IF_ERROR(ik_launch(norm_rope_append_kernel<TQ, TC>, T, 256, smem, stream, p, ldp, q_off, k_off, v_off, q_w, k_w, eps, \
                                  (TQ*)q_out, (TC*)k_pages, (TC*)v_pages, token_seq, token_pos, table, table_stride, inv_freq,  \
-                                 magnitude, nh, nkv, hd, hdv, rot, pairing, page_size, n_pages, write_cache, per_head, status))
+                                 magnitude, nh, nkv, hd, hdv, rot, pairing, page_size, n_pages, write_cache, per_head, bias, v_norm, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_NRA(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_NRA(__nv_bfloat16, __nv_bfloat16);
     else return IK_BAD_ARGUMENT;

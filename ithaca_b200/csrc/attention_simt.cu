@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(TILE)
 attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, const TC* __restrict__ v_pages,
                       TO* __restrict__ out, const int* __restrict__ token_seq, const int* __restrict__ token_pos,
                       const int* __restrict__ table, int table_stride, int nh, int nkv, int hd, int hdv, int ldv, float scale,
-                      float softcap, int window, int sink, int page_size, int n_pages, int* status) {
+                      float softcap, int window, int sink, const float* __restrict__ sink_v, int page_size, int n_pages, int* status) {
     ik_pdl_wait();
     ik_pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char smem[];
@@ -42,7 +42,8 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
     for (int i = tid; i < hd; i += TILE) qs[i] = ik_ld(qrow, i);
 
     // the sink stands at the head of the running softmax: a maximum of 0 whose weight exp(0 - 0) = 1 is already in the sum
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f, o[MAX_R];
+    // (with sink_v the sink's score is the head's own number instead of 0; it is not scaled)
+    float m = sink ? (sink_v ? sink_v[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f, o[MAX_R];
     #pragma unroll
     for (int r = 0; r < MAX_R; r++) o[r] = 0.f;
     __syncthreads();
@@ -104,7 +105,7 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_pages, 
 IK_EXPORT int ik_attention_simt(const void* q, int q_dtype, const void* k_pages, const void* v_pages, int cache_dtype,
                                 void* out, int out_dtype, const int* token_seq, const int* token_pos, const int* table,
                                 int table_stride, int T, int nh, int nkv, int hd, int hdv, int ldv, float scale, float softcap, int window,
-                                int sink, int page_size, int n_pages, int* status, cudaStream_t stream) {
+                                int sink, const float* sink_v, int page_size, int n_pages, int* status, cudaStream_t stream) {
     if (ldv < hdv) return IK_BAD_ARGUMENT;
     if (T < 0 || nh <= 0 || nkv <= 0 || nh % nkv || hd <= 0 || hdv <= 0 || hdv > TILE * MAX_R || page_size <= 0 || softcap < 0.f) return IK_BAD_ARGUMENT;
     if (q_dtype != out_dtype) return IK_BAD_ARGUMENT;
@@ -113,7 +114,7 @@ IK_EXPORT int ik_attention_simt(const void* q, int q_dtype, const void* k_pages,
     const size_t smem = (size_t)(hd + TILE + 32) * sizeof(float) + TILE * sizeof(size_t);
 #define IK_ATT(TQ, TC)                                                                                                \
     IK_RETURN_IF_ERROR(ik_launch(attention_simt_kernel<TQ, TC, TQ>, grid, TILE, smem, stream, (const TQ*)q, (const TC*)k_pages, (const TC*)v_pages, \
-        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, hdv, ldv, scale, softcap, window, sink, page_size, n_pages, status))
+        (TQ*)out, token_seq, token_pos, table, table_stride, nh, nkv, hd, hdv, ldv, scale, softcap, window, sink, sink_v, page_size, n_pages, status))
     if (q_dtype == IK_F32 && cache_dtype == IK_F32) IK_ATT(float, float);
     else if (q_dtype == IK_BF16 && cache_dtype == IK_BF16) IK_ATT(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == IK_F32 && cache_dtype == IK_BF16) IK_ATT(float, __nv_bfloat16);

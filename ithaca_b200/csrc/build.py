@@ -30,7 +30,7 @@ _COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcom
                  "--expt-relaxed-constexpr"]
 
 # The always-needed kernels.  Specialised modules are listed in SPECIALISED.
-CORE_SOURCES = ["elementwise.cu", "layernorm.cu", "short_conv.cu", "recurrent.cu", "delta.cu", "latent.cu", "attention_extras.cu", "moe.cu", "gemm_simt.cu", "gemm_mma.cu", "gemm_tcgen05.cu",
+CORE_SOURCES = ["elementwise.cu", "layernorm.cu", "short_conv.cu", "recurrent.cu", "delta.cu", "row_decay.cu", "hyper.cu", "latent.cu", "attention_extras.cu", "moe.cu", "gemm_simt.cu", "gemm_mma.cu", "gemm_tcgen05.cu",
                 "attention_simt.cu", "sampling.cu"]
 
 _lock = threading.Lock()

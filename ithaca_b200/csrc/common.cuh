@@ -69,7 +69,7 @@ __device__ __forceinline__ float ik_glu_fast(float g, float u, float alpha, floa
 
 // How a product's epilogue joins the gate and up halves of its rows: kind 0 = not at all, 1 = silu(g) * u, 2 = the gate
 // with parameters above.  It converts from and to the plain flag, so code that only asks "is there a join" reads as before.
-// A code of 16 + a means no join but an activation on every result: a = 0 relu(x)^2, a = 1 the tanh form of gelu (``act`` is a + 1).
+// A code of 16 + a means no join but an activation on every result: a = 0 relu(x)^2, a = 1 the tanh form of gelu, a = 2 tanh (``act`` is a + 1).
 struct IkGlu {
     int kind, act;
     float alpha, limit, shift;
@@ -77,9 +77,11 @@ struct IkGlu {
         : kind(k >= 16 ? 0 : k), act(k >= 16 ? k - 15 : 0), alpha(a), limit(l), shift(s) {}
     __host__ __device__ operator int() const { return kind; }
 };
-// Activation of an ungated feed-forward.  kind 0: relu(x)^2;  kind 1: gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).
+// Activation of an ungated feed-forward.  kind 0: relu(x)^2;  kind 1: gelu, tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)));
+// kind 2: tanh(x).
 __device__ __forceinline__ float ik_plain_act_value(float x, int kind) {
     if (kind == 0) { const float r = fmaxf(x, 0.f); return r * r; }
+    if (kind == 2) return tanhf(x);
     return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 __device__ __forceinline__ float ik_glu_act(const IkGlu& j, float v) { return j.act ? ik_plain_act_value(v, j.act - 1) : v; }

@@ -29,7 +29,8 @@ __device__ __forceinline__ void ik_cp_async_wait_all() { asm volatile("cp.async.
 // One block per token.  u [T, ldu] holds q (G heads of dk) from q_off and k from k_off, behind their convolution and
 // activation: every head becomes x / sqrt(sum x^2 + unit_eps), q also times q_mult, in place (one warp per head, lanes in
 // index order, then the shuffle tree).  p [T, ldp] holds the step's and the decay's projections, one column per head from
-// b_off and a_off: bg[t, 0, h] = sigmoid(p_b), bg[t, 1, h] = exp(-exp(A_log[h]) * softplus(p_a + dt_bias[h])).
+// b_off and a_off: bg[t, 0, h] = sigmoid(p_b), bg[t, 1, h] = exp(-exp(A_log[h]) * softplus(p_a + dt_bias[h])).  a_off < 0:
+// the decays are formed elsewhere (a decay per key channel) and bg[t, 1, :] is left alone.
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(float* __restrict__ u, int ldu, int q_off, int k_off, const float* __restrict__ p, int ldp, int b_off, int a_off,
                      const float* __restrict__ A_log, const float* __restrict__ dt_bias, float* __restrict__ bg, int G, int dk,
@@ -51,6 +52,7 @@ delta_prepare_kernel(float* __restrict__ u, int ldu, int q_off, int k_off, const
     for (int h = threadIdx.x; h < H; h += 128) {
         const float* row = p + (size_t)t * ldp;
         bg[((size_t)t * 2) * H + h] = 1.0f / (1.0f + expf(-row[b_off + h]));
+        if (a_off < 0) continue;
         const double z = (double)row[a_off + h] + (double)dt_bias[h];
         const double sp = z > 30.0 ? z : log1p(exp(z));
         bg[((size_t)t * 2 + 1) * H + h] = (float)exp(-exp((double)A_log[h]) * sp);
@@ -60,7 +62,7 @@ delta_prepare_kernel(float* __restrict__ u, int ldu, int q_off, int k_off, const
 IK_EXPORT int ik_delta_prepare(float* u, int ldu, int q_off, int k_off, const float* p, int ldp, int b_off, int a_off,
                                const float* A_log, const float* dt_bias, float* bg, int T, int G, int dk, int H, float q_mult,
                                float unit_eps, cudaStream_t stream) {
-    if (T < 0 || G <= 0 || dk <= 0 || H <= 0 || !u || !p || !A_log || !dt_bias || !bg) return IK_BAD_ARGUMENT;
+    if (T < 0 || G <= 0 || dk <= 0 || H <= 0 || !u || !p || (a_off >= 0 && (!A_log || !dt_bias)) || !bg) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     IK_RETURN_IF_ERROR(ik_launch(delta_prepare_kernel, T, 128, 0, stream, u, ldu, q_off, k_off, p, ldp, b_off, a_off, A_log, dt_bias, bg,
                                  G, dk, H, q_mult, unit_eps));
@@ -260,11 +262,12 @@ IK_EXPORT int ik_delta_rule(const float* u, int ldu, int q_off, int k_off, int v
 
 // ------------------------------------------------------------------ RMS norm per head with a gate
 // out[t, h*dv + i] = x[t, h, i] * (1 / sqrt(mean_i(x[t, h, :]^2) + eps)) * w[i] * act(p[t, g_off + h*dv + i]), the weight of
-// size dv shared by the heads; act 1: silu, 2: sigmoid, 0: no gate.  One warp per (token, head).
+// size dv shared by the heads (w_head = 0) or one of size dv per head (w_head = dv: w[h * dv + i]); act 1: silu, 2: sigmoid,
+// 0: no gate.  One warp per (token, head).
 template <typename TO>
 __global__ void __launch_bounds__(256)
 head_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ p, int ldp, int g_off,
-                      TO* __restrict__ out, int rows, int H, int dv, float eps, int act) {
+                      TO* __restrict__ out, int rows, int H, int dv, float eps, int act, int w_head) {
     ik_pdl_wait();
     IK_AFTER_WAIT(x);
     IK_AFTER_WAIT(p);
@@ -280,7 +283,7 @@ head_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w, 
     const float s = 1.0f / sqrtf(ss / (float)dv + eps);
     const float* g = act ? p + (size_t)t * ldp + g_off + h * dv : nullptr;
     for (int i = lane; i < dv; i += 32) {
-        float v = a[i] * s * w[i];
+        float v = a[i] * s * w[h * w_head + i];
         if (act == 1) v *= g[i] / (1.0f + expf(-g[i]));
         else if (act == 2) v *= 1.0f / (1.0f + expf(-g[i]));
         ik_st(out, (size_t)row * dv + i, v);
@@ -288,14 +291,14 @@ head_norm_gate_kernel(const float* __restrict__ x, const float* __restrict__ w, 
 }
 
 IK_EXPORT int ik_head_norm_gate(const float* x, const float* w, const float* p, int ldp, int g_off, void* out, int out_dtype, int T,
-                                int H, int dv, float eps, int act, cudaStream_t stream) {
-    if (T < 0 || H <= 0 || dv <= 0 || act < 0 || act > 2 || (act && !p)) return IK_BAD_ARGUMENT;
+                                int H, int dv, float eps, int act, int w_head, cudaStream_t stream) {
+    if (T < 0 || H <= 0 || dv <= 0 || act < 0 || act > 2 || (act && !p) || (w_head != 0 && w_head != dv)) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const int rows = T * H, blocks = (rows + 7) / 8;
     if (out_dtype == IK_F32)
-        IK_RETURN_IF_ERROR(ik_launch(head_norm_gate_kernel<float>, blocks, 256, 0, stream, x, w, p, ldp, g_off, (float*)out, rows, H, dv, eps, act));
+        IK_RETURN_IF_ERROR(ik_launch(head_norm_gate_kernel<float>, blocks, 256, 0, stream, x, w, p, ldp, g_off, (float*)out, rows, H, dv, eps, act, w_head));
     else if (out_dtype == IK_BF16)
-        IK_RETURN_IF_ERROR(ik_launch(head_norm_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, w, p, ldp, g_off, (__nv_bfloat16*)out, rows, H, dv, eps, act));
+        IK_RETURN_IF_ERROR(ik_launch(head_norm_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, w, p, ldp, g_off, (__nv_bfloat16*)out, rows, H, dv, eps, act, w_head));
     else return IK_BAD_ARGUMENT;
     IK_LAUNCH_STATUS();
 }

@@ -244,7 +244,7 @@ __global__ void plain_act_kernel(const float* __restrict__ x, TO* __restrict__ o
 }
 
 IK_EXPORT int ik_plain_act(const float* x, void* out, int out_dtype, unsigned long long total, int kind, cudaStream_t stream) {
-    if (kind < 0 || kind > 1) return IK_BAD_ARGUMENT;
+    if (kind < 0 || kind > 2) return IK_BAD_ARGUMENT;
     if (total == 0) return IK_OK;
     const int blocks = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
     if (out_dtype == IK_F32) IK_RETURN_IF_ERROR(ik_launch(plain_act_kernel<float>, blocks, 256, 0, stream, x, (float*)out, (size_t)total, kind));

@@ -81,7 +81,10 @@ IK_EXPORT int ik_latent_prepare(const float* p, int ldp, int q_off, int c_off, c
                                 int q_dtype, void* k_pages, int cache_dtype, const int* token_seq, const int* token_pos,
                                 const int* table, int table_stride, const float* inv_freq, int T, int H, int dk, int dr, int rank,
                                 int page_size, int n_pages, int write_cache, int* status, cudaStream_t stream) {
-    if (T < 0 || H <= 0 || dk <= 0 || dr <= 0 || (dr & 1) || rank <= 0 || page_size <= 0 || !inv_freq) return IK_BAD_ARGUMENT;
+    // H = 0: the queries are made elsewhere (behind a latent of their own) and only the row is written; dr = 0: no turning part
+    if (T < 0 || H < 0 || (H > 0 && (dk <= 0 || !q_plain || (dr > 0 && !q_full))) || dr < 0 || (dr & 1) || rank <= 0 || page_size <= 0 ||
+        (dr > 0 && !inv_freq))
+        return IK_BAD_ARGUMENT;
     if (write_cache && (!c_w || !k_pages)) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const size_t smem = (size_t)dr * sizeof(float);

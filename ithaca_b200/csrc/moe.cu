@@ -2,7 +2,8 @@
 // over those groups, and the weighted sum of a token's choices.
 //
 //   router    the router's logits z = Wr x (float products, float sums) and the routing below, in one kernel.
-//   route     (the routing alone, from ready-made logits) scores = softmax(router logits) over all experts (float).  Experts form `n_groups` equal groups of
+//   route     (the routing alone, from ready-made logits) scores = softmax(router logits) over all experts (float), or with
+//             score = 1 the sigmoid of every logit by itself.  Experts form `n_groups` equal groups of
 //             neighbours; a group counts by its best score, only experts of the `keep` best groups can be chosen
 //             (n_groups <= 1: all can), and the `top` best of them are.  The weights are the chosen experts' scores as
 //             they are, or divided by their sum (renorm).  Equal scores: the lower index wins.
@@ -32,15 +33,19 @@ constexpr int MOE_BM = 64, MOE_BN = 64, MOE_BK = 16, MOE_TM = 4, MOE_TN = 4;
 // One warp routes one token.  sc [E]: the token's router logits on entry (any memory the warp may write), its scores
 // with the taken ones marked on exit; gb [n_groups]: scratch.
 __device__ __forceinline__ void route_token(float* sc, float* gb, int lane, int* __restrict__ chosen, float* __restrict__ weight,
-                                            int E, int top, int ng, int keep, int renorm) {
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - m); sc[e] = p; sum += p; }
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) sc[e] *= inv;
+                                            int E, int top, int ng, int keep, int renorm, int score) {
+    if (score == 1) {                 // every expert's score is the sigmoid of its own logit
+        for (int e = lane; e < E; e += 32) sc[e] = 1.0f / (1.0f + expf(-sc[e]));
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) { const float p = expf(sc[e] - m); sc[e] = p; sum += p; }
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) sc[e] *= inv;
+    }
     __syncwarp();
     // warp-wide argmax over n values v(i) >= 0 (taken ones are marked -1); the lower index wins a tie
     auto argmax = [&](const float* v, int n) -> int {
@@ -85,7 +90,7 @@ __device__ __forceinline__ void route_token(float* sc, float* gb, int lane, int*
 // From ready-made logits: one warp per token.  smem: scores [E] then group bests [n_groups] per warp.
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
-                 int top, int n_groups, int keep, int renorm) {
+                 int top, int n_groups, int keep, int renorm, int score) {
     ik_pdl_wait();
     IK_AFTER_WAIT(logits);
     ik_pdl_launch_dependents();
@@ -97,7 +102,7 @@ moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, flo
     float* sc = sm + (size_t)warp * (E + ng);
     for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
     __syncwarp();
-    route_token(sc, sc + E, lane, chosen + (size_t)t * top, weight + (size_t)t * top, E, top, ng, keep, renorm);
+    route_token(sc, sc + E, lane, chosen + (size_t)t * top, weight + (size_t)t * top, E, top, ng, keep, renorm, score);
 }
 
 // The router's product and the routing in one kernel.  A block takes TOK tokens: their activations go to shared memory
@@ -109,7 +114,7 @@ moe_route_kernel(const float* __restrict__ logits, int* __restrict__ chosen, flo
 template <int TOK, int THREADS, typename TX>
 __global__ void __launch_bounds__(THREADS)
 moe_router_kernel(const TX* __restrict__ x, const float* __restrict__ wr, int* __restrict__ chosen, float* __restrict__ weight,
-                  int T, int K, int E, int top, int n_groups, int keep, int renorm, int ldx) {
+                  int T, int K, int E, int top, int n_groups, int keep, int renorm, int score, int ldx) {
     ik_pdl_wait();
     IK_AFTER_WAIT(x);
     ik_pdl_launch_dependents();
@@ -186,7 +191,7 @@ moe_router_kernel(const TX* __restrict__ x, const float* __restrict__ wr, int* _
         const int t = t0 + i;
         if (t >= T) continue;
         float* sc = lg + (size_t)i * (E + ng);
-        route_token(sc, sc + E, lane, chosen + (size_t)t * top, weight + (size_t)t * top, E, top, ng, keep, renorm);
+        route_token(sc, sc + E, lane, chosen + (size_t)t * top, weight + (size_t)t * top, E, top, ng, keep, renorm, score);
     }
 }
 
@@ -230,7 +235,7 @@ template <typename TX, typename TW, typename TY, int MODE>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restrict__ Y, const int* __restrict__ offsets,
                 const int* __restrict__ sorted, const int* __restrict__ tiles, const int* __restrict__ n_tiles, int top,
-                int N, int K, int ldx, int ldy) {
+                int N, int K, int ldx, int ldy, const float* __restrict__ row_scale, int act) {
     ik_pdl_wait();
     IK_AFTER_WAIT(X);
     IK_AFTER_WAIT(offsets);
@@ -243,6 +248,7 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
     __shared__ float xs[MOE_BK][MOE_BM + 1];
     __shared__ float ws[NW][MOE_BK][MOE_BN + 1];
     __shared__ int src_row[MOE_BM], dst_row[MOE_BM];
+    __shared__ float in_scale[MOE_BM];
     const int e = tiles[2 * blockIdx.y], p0 = tiles[2 * blockIdx.y + 1];
     const int rows = min(MOE_BM, offsets[e + 1] - p0);
     const int n0 = blockIdx.x * MOE_BN;
@@ -251,8 +257,9 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
     if (threadIdx.x < MOE_BM) {
         const int r = threadIdx.x;
         const int a = r < rows ? sorted[p0 + r] : -1;
-        src_row[r] = a < 0 ? -1 : (MODE == 0 ? a / top : p0 + r);
-        dst_row[r] = a < 0 ? -1 : (MODE == 0 ? p0 + r : a);
+        src_row[r] = a < 0 ? -1 : (MODE != 1 ? a / top : p0 + r);
+        dst_row[r] = a < 0 ? -1 : (MODE != 1 ? p0 + r : a);
+        in_scale[r] = (a >= 0 && row_scale) ? row_scale[a] : 1.0f;
     }
     __syncthreads();
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
@@ -269,7 +276,7 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
             const int idx = threadIdx.x + l * 256;
             const int r = idx / MOE_BK, c = idx % MOE_BK, k = k0 + c;
             const int sr = src_row[r];
-            xs[c][r] = (sr >= 0 && k < K) ? ik_ld(X, (size_t)sr * ldx + k) : 0.f;
+            xs[c][r] = (sr >= 0 && k < K) ? (MODE == 2 ? ik_round_to<TX>(ik_ld(X, (size_t)sr * ldx + k) * in_scale[r]) : ik_ld(X, (size_t)sr * ldx + k)) : 0.f;
             #pragma unroll
             for (int w = 0; w < NW; w++)
                 ws[w][c][r] = (n0 + r < N && k < K) ? ik_ld(We, ((size_t)(MODE == 0 ? 2 : 1) * (n0 + r) + w) * K + k) : 0.f;
@@ -301,7 +308,7 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
         for (int j = 0; j < MOE_TN; j++) {
             const int n = n0 + tx + 16 * j;
             if (n >= N) continue;
-            const float v = MODE == 0 ? ik_swiglu(acc[0][i][j], acc[NW - 1][i][j]) : acc[0][i][j];
+            const float v = MODE == 0 ? ik_swiglu(acc[0][i][j], acc[NW - 1][i][j]) : MODE == 2 ? ik_plain_act_value(acc[0][i][j], act) : acc[0][i][j];
             ik_st(Y, (size_t)dr * ldy + n, v);
         }
     }
@@ -311,7 +318,7 @@ moe_gemm_kernel(const TX* __restrict__ X, const TW* __restrict__ W, TY* __restri
 // One block.  row_of [A], src_token [n_tiles * bn], tile_group [n_tiles].
 __global__ void __launch_bounds__(1024)
 moe_sort_padded_kernel(const int* __restrict__ chosen, int* __restrict__ row_of, int* __restrict__ src_token,
-                       int* __restrict__ tile_group, int A, int E, int top, int bn, int n_tiles) {
+                       int* __restrict__ tile_group, int A, int E, int top, int bn, int n_tiles, int* __restrict__ src_assign) {
     ik_pdl_wait();
     IK_AFTER_WAIT(chosen);
     ik_pdl_launch_dependents();
@@ -339,7 +346,10 @@ moe_sort_padded_kernel(const int* __restrict__ chosen, int* __restrict__ row_of,
         if (e < 0 || e >= E) { row_of[a] = 0; continue; }
         const int r = atomicAdd(&cur[e], 1);
         row_of[a] = r;
-        if (r < n_tiles * bn) src_token[r] = a / top;
+        if (r < n_tiles * bn) {
+            src_token[r] = a / top;
+            if (src_assign) src_assign[r] = a;            // (read only where src_token is not -1)
+        }
     }
 }
 
@@ -358,6 +368,32 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __rest
     }
 }
 
+// The same with every row multiplied by the weight of its assignment (in float, rounded once): xp[r, :] = x[src_token[r], :] *
+// weight[src_assign[r]].
+__global__ void moe_gather_scaled_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ src_token,
+                                         const int* __restrict__ src_assign, const float* __restrict__ weight,
+                                         __nv_bfloat16* __restrict__ xp, int rows, int d) {
+    ik_pdl_wait();
+    IK_AFTER_WAIT(x);
+    IK_AFTER_WAIT(src_token);
+    IK_AFTER_WAIT(src_assign);
+    IK_AFTER_WAIT(weight);
+    ik_pdl_launch_dependents();
+    const int d4 = d / 4;
+    const size_t total = (size_t)rows * d4, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const size_t r = idx / d4;
+        const int c = (int)(idx - r * d4) * 4, t = src_token[r];
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (t >= 0) {
+            const float w = weight[src_assign[r]];
+            v = ik_ld4(x, (size_t)t * d + c);
+            v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+        }
+        ik_st4(xp, r * d + c, v);
+    }
+}
+
 // ------------------------------------------------------------------------------------------ combine
 __global__ void moe_combine_kernel(const float* __restrict__ parts, const float* __restrict__ weight, const int* __restrict__ row_of,
                                    float* __restrict__ y, int T, int top, int d) {
@@ -371,7 +407,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ parts, const float*
         const size_t t = idx / d;
         const int i = (int)(idx - t * d);
         float acc = 0.f;
-        for (int k = 0; k < top; k++) acc = fmaf(weight[t * top + k], parts[(size_t)(row_of ? row_of[t * top + k] : t * top + k) * d + i], acc);
+        for (int k = 0; k < top; k++) acc = fmaf(weight ? weight[t * top + k] : 1.0f, parts[(size_t)(row_of ? row_of[t * top + k] : t * top + k) * d + i], acc);
         y[idx] = acc;
     }
 }
@@ -379,10 +415,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ parts, const float*
 template <int MODE>
 int launch_gemm(const void* X, int x_dtype, const void* W, int w_dtype, void* Y, int y_dtype, const int* offsets,
                 const int* sorted, const int* tiles, const int* n_tiles, int max_tiles, int top, int N, int K, int ldx,
-                int ldy, cudaStream_t stream) {
+                int ldy, const float* row_scale, int act, cudaStream_t stream) {
     dim3 grid((N + MOE_BN - 1) / MOE_BN, max_tiles);
 #define IK_MOE(TX, TW, TY) \
-    IK_RETURN_IF_ERROR(ik_launch(moe_gemm_kernel<TX, TW, TY, MODE>, grid, 256, 0, stream, (const TX*)X, (const TW*)W, (TY*)Y, offsets, sorted, tiles, n_tiles, top, N, K, ldx, ldy))
+    IK_RETURN_IF_ERROR(ik_launch(moe_gemm_kernel<TX, TW, TY, MODE>, grid, 256, 0, stream, (const TX*)X, (const TW*)W, (TY*)Y, offsets, sorted, tiles, n_tiles, top, N, K, ldx, ldy, row_scale, act))
     const int code = x_dtype * 4 + w_dtype * 2 + y_dtype;
     switch (code) {
         case 0: IK_MOE(float, float, float); break;
@@ -400,19 +436,19 @@ int launch_gemm(const void* X, int x_dtype, const void* W, int w_dtype, void* Y,
 IK_EXPORT int ik_moe_tile_rows() { return MOE_BM; }
 
 IK_EXPORT int ik_moe_route(const float* logits, int* chosen, float* weight, int T, int E, int top, int n_groups, int keep,
-                           int renorm, cudaStream_t stream) {
+                           int renorm, int score, cudaStream_t stream) {
     if (T < 0 || E <= 0 || top <= 0 || top > E) return IK_BAD_ARGUMENT;
     if (n_groups > 1 && (E % n_groups || keep <= 0 || keep > n_groups || top > keep * (E / n_groups))) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
     const size_t smem = 4 * (size_t)(E + (n_groups > 1 ? n_groups : 0)) * sizeof(float);
     if (smem > 48 * 1024) return IK_UNSUPPORTED;
-    IK_RETURN_IF_ERROR(ik_launch(moe_route_kernel, (T + 3) / 4, 128, smem, stream, logits, chosen, weight, T, E, top, n_groups, keep, renorm));
+    IK_RETURN_IF_ERROR(ik_launch(moe_route_kernel, (T + 3) / 4, 128, smem, stream, logits, chosen, weight, T, E, top, n_groups, keep, renorm, score));
     IK_LAUNCH_STATUS();
 }
 
 // x [T, K] (float or bfloat16, rows ldx apart), wr [E, K] float -> chosen, weight [T, top]
 IK_EXPORT int ik_moe_router(const void* x, int x_dtype, const float* wr, int* chosen, float* weight, int T, int K, int E, int top,
-                            int n_groups, int keep, int renorm, int ldx, cudaStream_t stream) {
+                            int n_groups, int keep, int renorm, int score, int ldx, cudaStream_t stream) {
     if (T < 0 || E <= 0 || K <= 0 || top <= 0 || top > E || ldx < K) return IK_BAD_ARGUMENT;
     if (n_groups > 1 && (E % n_groups || keep <= 0 || keep > n_groups || top > keep * (E / n_groups))) return IK_BAD_ARGUMENT;
     if (K % 4 || ((uintptr_t)wr % 16)) return IK_UNSUPPORTED;
@@ -432,7 +468,7 @@ IK_EXPORT int ik_moe_router(const void* x, int x_dtype, const float* wr, int* ch
             if (e0 != cudaSuccess) return (int)e0;                                                                         \
         }                                                                                                                  \
         IK_RETURN_IF_ERROR(ik_launch(kern, (T + TOK - 1) / TOK, THREADS, smem, stream, (const TX*)x, wr, chosen, weight, T, K, E, top, \
-                                     n_groups, keep, renorm, ldx));                                                        \
+                                     n_groups, keep, renorm, score, ldx));                                                        \
     }
     if (x_dtype == IK_F32) { if (tok == 1) IK_ROUTER(1, float) else if (tok == 4) IK_ROUTER(4, float) else IK_ROUTER(8, float) }
     else if (x_dtype == IK_BF16) { if (tok == 1) IK_ROUTER(1, __nv_bfloat16) else if (tok == 4) IK_ROUTER(4, __nv_bfloat16) else IK_ROUTER(8, __nv_bfloat16) }
@@ -449,24 +485,28 @@ IK_EXPORT int ik_moe_sort(const int* chosen, int* offsets, int* sorted, int* til
     IK_LAUNCH_STATUS();
 }
 
+// mode 2: X [T, K] tokens, each row times row_scale[assignment] (rounded to X's type) as it is read, W [E, N, K], Y [A, N] =
+// act(product) at sorted places (act 0: relu(x)^2, 1: gelu, tanh form).
 // mode 0: X [T, K] tokens, W [E, 2N, K] (gate j, up j in rows 2j, 2j + 1), Y [A, N] = silu(gate) * up at sorted places.  mode 1: X [A, K] at sorted
 // places, W [E, N, K], Y [A, N] at the assignments' rows.
 IK_EXPORT int ik_moe_gemm(int mode, const void* X, int x_dtype, const void* W, int w_dtype, void* Y, int y_dtype,
                           const int* offsets, const int* sorted, const int* tiles, const int* n_tiles, int max_tiles, int top,
-                          int N, int K, int ldx, int ldy, cudaStream_t stream) {
+                          int N, int K, int ldx, int ldy, const float* row_scale, int act, cudaStream_t stream) {
     if (max_tiles < 0 || top <= 0 || N <= 0 || K <= 0 || ldx < K || ldy < N || max_tiles > 65535) return IK_BAD_ARGUMENT;
     if (max_tiles == 0) return IK_OK;
-    if (mode == 0) return launch_gemm<0>(X, x_dtype, W, w_dtype, Y, y_dtype, offsets, sorted, tiles, n_tiles, max_tiles, top, N, K, ldx, ldy, stream);
-    if (mode == 1) return launch_gemm<1>(X, x_dtype, W, w_dtype, Y, y_dtype, offsets, sorted, tiles, n_tiles, max_tiles, top, N, K, ldx, ldy, stream);
+    if (mode == 0) return launch_gemm<0>(X, x_dtype, W, w_dtype, Y, y_dtype, offsets, sorted, tiles, n_tiles, max_tiles, top, N, K, ldx, ldy, nullptr, 0, stream);
+    if (mode == 1) return launch_gemm<1>(X, x_dtype, W, w_dtype, Y, y_dtype, offsets, sorted, tiles, n_tiles, max_tiles, top, N, K, ldx, ldy, nullptr, 0, stream);
+    if (mode == 2 && act >= 0 && act <= 1)
+        return launch_gemm<2>(X, x_dtype, W, w_dtype, Y, y_dtype, offsets, sorted, tiles, n_tiles, max_tiles, top, N, K, ldx, ldy, row_scale, act, stream);
     return IK_BAD_ARGUMENT;
 }
 
 IK_EXPORT int ik_moe_sort_padded(const int* chosen, int* row_of, int* src_token, int* tile_group, int A, int E, int top, int bn,
-                                 int n_tiles, cudaStream_t stream) {
+                                 int n_tiles, int* src_assign, cudaStream_t stream) {
     if (A < 0 || E <= 0 || top <= 0 || bn <= 0 || n_tiles < 0 || n_tiles < (A / bn + E < A ? A / bn + E : A)) return IK_BAD_ARGUMENT;
     if ((size_t)2 * E * sizeof(int) > 48 * 1024) return IK_UNSUPPORTED;
     IK_RETURN_IF_ERROR(ik_launch(moe_sort_padded_kernel, 1, 1024, (size_t)2 * E * sizeof(int), stream, chosen, row_of, src_token, tile_group, A, E,
-                                 top, bn, n_tiles));
+                                 top, bn, n_tiles, src_assign));
     IK_LAUNCH_STATUS();
 }
 
@@ -478,7 +518,17 @@ IK_EXPORT int ik_moe_gather(const void* x, const int* src_token, void* xp, int r
     IK_LAUNCH_STATUS();
 }
 
-// row_of: where assignment a's result lies in `parts` (nullptr: at row a)
+IK_EXPORT int ik_moe_gather_scaled(const void* x, const int* src_token, const int* src_assign, const float* weight, void* xp, int rows,
+                                   int d, cudaStream_t stream) {
+    if (rows < 0 || d <= 0 || d % 8 || ((uintptr_t)x % 16) || ((uintptr_t)xp % 16) || !src_assign || !weight) return IK_BAD_ARGUMENT;
+    if (rows == 0) return IK_OK;
+    const size_t total = (size_t)rows * (d / 4), want = (total + 255) / 256, cap = (size_t)ik_sm_count() * 16;
+    IK_RETURN_IF_ERROR(ik_launch(moe_gather_scaled_kernel, (int)(want < cap ? want : cap), 256, 0, stream, (const __nv_bfloat16*)x, src_token,
+                                 src_assign, weight, (__nv_bfloat16*)xp, rows, d));
+    IK_LAUNCH_STATUS();
+}
+
+// row_of: where assignment a's result lies in `parts` (nullptr: at row a); weight nullptr: every weight is 1
 IK_EXPORT int ik_moe_combine(const float* parts, const float* weight, const int* row_of, float* y, int T, int top, int d, cudaStream_t stream) {
     if (T < 0 || top <= 0 || d <= 0) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;

@@ -85,13 +85,13 @@ _SIGNATURES = {
     "ik_rope_table": [_vp, _vp, _vp, _i, _i, _vp],
     "ik_gemm_qkv_rope_mma": [_vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_gemm_qkv_rope_tcgen05": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp],
-    "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _i, _vp, _vp],
+    "ik_attention_simt": [_vp, _i, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _vp, _i, _i, _vp, _vp],
     "ik_gemm_simt_batched": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _u64, _u64, _u64, _vp],
     "ik_scale_add_norm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
     "ik_plain_act": [_vp, _vp, _i, _u64, _i, _vp],
     "ik_delta_prepare": [_vp, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp],
     "ik_delta_rule": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_head_norm_gate": [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "ik_head_norm_gate": [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "ik_latent_prepare": [_vp, _i, _i, _i, _vp, _f, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                           _vp, _vp],
     "ik_layernorm": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _f, _vp],
@@ -99,13 +99,14 @@ _SIGNATURES = {
     "ik_conv_rope_append": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i,
                             _i, _i, _i, _i, _i, _vp, _vp],
     "ik_moe_tile_rows": [],
-    "ik_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "ik_moe_router": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_route": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_router": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_moe_sort": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
-    "ik_moe_gemm": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_gemm": [_i, _vp, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
     "ik_moe_combine": [_vp, _vp, _vp, _vp, _i, _i, _i, _vp],
-    "ik_moe_sort_padded": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "ik_moe_sort_padded": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_moe_gather": [_vp, _vp, _vp, _i, _i, _vp],
+    "ik_moe_gather_scaled": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "ik_gemm_tcgen05_grouped": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     "ik_argmax": [_vp, _i, _vp, _i, _i, _vp, _vp],
     "ik_argmax_scratch_bytes": [],
@@ -121,9 +122,18 @@ _SIGNATURES = {
     "ik_selective_scan": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "ik_decay_attention": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "ik_norm_rope_append": [_vp, _i, _i, _i, _i, _vp, _vp, _f, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _i, _i,
-                            _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+                            _i, _i, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp],
     "ik_head_gate": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "ik_gated_rmsnorm": [_vp, _vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _vp],
+    "ik_hyper_start": [_vp, _vp, _i, _i, _i, _vp],
+    "ik_add_rows": [_vp, _vp, _i, _i, _vp],
+    "ik_hyper_read": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp],
+    "ik_hyper_write": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp],
+    "ik_branch_norm_sum": [_vp, _vp, _vp, _vp, _i, _vp, _i, _i, _f, _i, _vp],
+    "ik_rmsnorm_range": [_vp, _i, _vp, _vp, _i, _i, _i, _f, _vp],
+    "ik_decay_rows": [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "ik_token_shift": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _u64, _i, _i, _i, _i, _i, _vp],
+    "ik_row_decay": [_i, _vp, _i, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
 }
 
 _lib = None
@@ -598,13 +608,27 @@ def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, k_pages
     return True
 
 
+def sink_flag(sink) -> int:
+    return 0 if sink is None or sink is False else 1
+
+
+def sink_values(sink, n_heads: int) -> Optional[torch.Tensor]:
+    """A sink is False / None (none), True (one more key of score 0) or a float32 tensor with every head's score."""
+    if not isinstance(sink, torch.Tensor):
+        return None
+    if sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous():
+        raise KernelError("attention: the sink needs one float32 score per head")
+    return sink
+
+
 def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,
                    token_pos: torch.Tensor, table: torch.Tensor, n_heads: int, scale: float, window: int,
-                   status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, softcap: float = 0.0, sink: bool = False,
+                   status: Optional[torch.Tensor], out: Optional[torch.Tensor] = None, softcap: float = 0.0, sink=False,
                    values_in_keys: int = 0) -> torch.Tensor:
     """``softcap``: scores become cap * tanh(score / cap) after the scale (0 = no cap).  The value pages may
     have a head size of their own; the output is then [T, n_heads * that size].  ``sink``: one more key of score 0
-    that carries no value (the weights are exp(s_j) / (1 + sum exp(s_j))).  ``values_in_keys`` = n > 0: a key row's
+    that carries no value (the weights are exp(s_j) / (1 + sum exp(s_j))); a float32 tensor [n_heads] instead of True gives
+    every head's sink a score of its own (not scaled).  ``values_in_keys`` = n > 0: a key row's
     leading n columns are its value (``v_pages`` is not read)."""
     _need(q, "q")
     _need(k_pages, "k_pages")
@@ -625,8 +649,8 @@ def attention_simt(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
     _work(f"attention_simt {T}x{n_heads}", _nbytes(q, out))
     _check(lib().ik_attention_simt(_ptr(q), _code(q), _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(out),
                                    _code(out), _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), T,
-                                   n_heads, nkv, hd, hdv, ldv, scale, softcap, window, 1 if sink else 0, page_size, n_pages,
-                                   _ptr(status), _stream()),
+                                   n_heads, nkv, hd, hdv, ldv, scale, softcap, window, sink_flag(sink), _ptr(sink_values(sink, n_heads)),
+                                   page_size, n_pages, _ptr(status), _stream()),
            "attention_simt")
     return out
 
@@ -705,20 +729,24 @@ def conv_rope_append(qkv: torch.Tensor, conv_w: Optional[torch.Tensor], ring: Op
                                      1 if write_cache else 0, _ptr(status), _stream()), "conv_rope_append", kernels=2 if taps > 1 else 1)
 
 
-def moe_route(logits: torch.Tensor, top: int, n_groups: int = 0, keep: int = 0, renorm: bool = False):
-    """Softmax scores over the experts and the ``top`` best among the ``keep`` best of ``n_groups`` groups of
+MOE_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_route(logits: torch.Tensor, top: int, n_groups: int = 0, keep: int = 0, renorm: bool = False, score: str = "softmax"):
+    """Scores over the experts (``score``: the softmax over all logits, or the sigmoid of each by itself) and the ``top`` best among the ``keep`` best of ``n_groups`` groups of
     neighbours (0 groups: among all).  Returns (chosen int32 [T, top], weights float [T, top])."""
     _need(logits, "logits", torch.float32)
     T, E = logits.shape
     chosen = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weight = torch.empty((T, top), dtype=torch.float32, device=logits.device)
     _work(f"moe_route {T}x{E}", _nbytes(logits, chosen, weight))
-    _check(lib().ik_moe_route(_ptr(logits), _ptr(chosen), _ptr(weight), T, E, top, n_groups, keep, 1 if renorm else 0, _stream()),
-           "moe_route")
+    _check(lib().ik_moe_route(_ptr(logits), _ptr(chosen), _ptr(weight), T, E, top, n_groups, keep, 1 if renorm else 0,
+                              MOE_SCORES[score], _stream()), "moe_route")
     return chosen, weight
 
 
-def moe_router(x: torch.Tensor, router: torch.Tensor, top: int, n_groups: int = 0, keep: int = 0, renorm: bool = False):
+def moe_router(x: torch.Tensor, router: torch.Tensor, top: int, n_groups: int = 0, keep: int = 0, renorm: bool = False,
+               score: str = "softmax"):
     """The router's logits ``x router^T`` (float products and sums, whatever type ``x`` has) and the routing of
     ``moe_route``, in one kernel.  Returns (chosen int32 [T, top], weights float [T, top]), or None when the kernel does
     not take these sizes (the caller forms the logits with a product and routes them)."""
@@ -732,7 +760,7 @@ def moe_router(x: torch.Tensor, router: torch.Tensor, top: int, n_groups: int = 
     weight = torch.empty((T, top), dtype=torch.float32, device=x.device)
     _work(f"moe_router {T}x{E}x{K}", T * K * x.element_size() + E * K * 4 + 8 * T * top, 2 * T * E * K)
     st = lib().ik_moe_router(_ptr(x), _code(x), _ptr(router), _ptr(chosen), _ptr(weight), T, K, E, top, n_groups, keep,
-                             1 if renorm else 0, x.stride(0), _stream())
+                             1 if renorm else 0, MOE_SCORES[score], x.stride(0), _stream())
     if st == -2:
         return None
     _check(st, "moe_router")
@@ -763,8 +791,10 @@ def moe_sort(chosen: torch.Tensor, n_experts: int) -> MoEPlan:
     return p
 
 
-def moe_gemm(mode: int, x: torch.Tensor, w: torch.Tensor, plan: MoEPlan, out_dtype: torch.dtype) -> torch.Tensor:
-    """Mode 0: ``x`` [T, d] tokens, ``w`` [E, 2 ff, d] (gate j and up j in rows 2j and 2j + 1) -> silu(gate) * up [A, ff] in sorted
+def moe_gemm(mode: int, x: torch.Tensor, w: torch.Tensor, plan: MoEPlan, out_dtype: torch.dtype,
+             row_scale: Optional[torch.Tensor] = None, act: Optional[str] = None) -> torch.Tensor:
+    """Mode 2: ``x`` [T, d] tokens, every row times ``row_scale`` [T, top] of its assignment as it is read, ``w`` [E, ff, d] ->
+    ``act`` (one of ``PLAIN_ACTS``) of the product, [A, ff] in sorted order.  Mode 0: ``x`` [T, d] tokens, ``w`` [E, 2 ff, d] (gate j and up j in rows 2j and 2j + 1) -> silu(gate) * up [A, ff] in sorted
     order.  Mode 1: ``x`` [A, ff] in sorted order, ``w`` [E, d, ff] -> [A, d], row t * top + k for token t's choice k."""
     _need(x, "x")
     _need(w, "w")
@@ -778,13 +808,13 @@ def moe_gemm(mode: int, x: torch.Tensor, w: torch.Tensor, plan: MoEPlan, out_dty
           2 * A * rows * K)
     _check(lib().ik_moe_gemm(mode, _ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _ptr(plan.offsets),
                              _ptr(plan.sorted), _ptr(plan.tiles), _ptr(plan.n_tiles), plan.max_tiles, plan.top, N, K,
-                             x.stride(0), out.stride(0), _stream()), "moe_gemm")
+                             x.stride(0), out.stride(0), _ptr(row_scale), PLAIN_ACTS[act] if act is not None else 0, _stream()), "moe_gemm")
     return out
 
 
 class MoEPaddedPlan:
     """A step's (token, choice) pairs in padded order: every expert's rows start at a multiple of the tile height."""
-    __slots__ = ("row_of", "src_token", "tile_group", "n_tiles", "bn", "rows", "top", "n_experts")
+    __slots__ = ("row_of", "src_token", "src_assign", "tile_group", "n_tiles", "bn", "rows", "top", "n_experts")
 
 
 def moe_sort_padded(chosen: torch.Tensor, n_experts: int, bn: int) -> MoEPaddedPlan:
@@ -795,26 +825,33 @@ def moe_sort_padded(chosen: torch.Tensor, n_experts: int, bn: int) -> MoEPaddedP
     p.top, p.n_experts, p.bn = top, n_experts, bn
     p.n_tiles = min(A, A // bn + n_experts)              # a tile holds at least one row; an expert wastes less than one tile
     p.rows = p.n_tiles * bn
-    meta = torch.empty(A + p.rows + p.n_tiles, dtype=torch.int32, device=chosen.device)
-    p.row_of, p.src_token, p.tile_group = meta[:A], meta[A:A + p.rows], meta[A + p.rows:]
+    meta = torch.empty(A + 2 * p.rows + p.n_tiles, dtype=torch.int32, device=chosen.device)
+    p.row_of, p.src_token, p.tile_group = meta[:A], meta[A:A + p.rows], meta[A + p.rows:A + p.rows + p.n_tiles]
+    p.src_assign = meta[A + p.rows + p.n_tiles:]
     _work(f"moe_sort_padded {A}", 8 * A + 4 * p.rows)
     _check(lib().ik_moe_sort_padded(_ptr(chosen), _ptr(p.row_of), _ptr(p.src_token), _ptr(p.tile_group), A, n_experts, top, bn,
-                                    p.n_tiles, _stream()), "moe_sort_padded")
+                                    p.n_tiles, _ptr(p.src_assign), _stream()), "moe_sort_padded")
     return p
 
 
-def moe_gather(x: torch.Tensor, plan: MoEPaddedPlan) -> torch.Tensor:
-    """The tokens' activations in padded order [rows, d] (bfloat16; padding rows zero)."""
+def moe_gather(x: torch.Tensor, plan: MoEPaddedPlan, weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The tokens' activations in padded order [rows, d] (bfloat16; padding rows zero).  ``weight`` [T, top] float: every row
+    is multiplied by the weight of its assignment (in float, rounded once)."""
     _need(x, "x", torch.bfloat16)
     d = x.shape[1]
     out = torch.empty((plan.rows, d), dtype=torch.bfloat16, device=x.device)
     _work(f"moe_gather {plan.rows}x{d}", 4 * plan.rows * d)
+    if weight is not None:
+        _need(weight, "weight", torch.float32)
+        _check(lib().ik_moe_gather_scaled(_ptr(x), _ptr(plan.src_token), _ptr(plan.src_assign), _ptr(weight), _ptr(out), plan.rows, d,
+                                          _stream()), "moe_gather")
+        return out
     _check(lib().ik_moe_gather(_ptr(x), _ptr(plan.src_token), _ptr(out), plan.rows, d, _stream()), "moe_gather")
     return out
 
 
 def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, plan: MoEPaddedPlan, out_dtype: torch.dtype, swiglu: bool = False,
-                         status: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                         status: Optional[torch.Tensor] = None, act: Optional[str] = None) -> Optional[torch.Tensor]:
     """``x`` [rows, K] in padded order, ``w`` [E * N, K]: the stacked matrices of the experts; token tile i of ``plan.bn``
     rows multiplies matrix ``plan.tile_group[i]``.  Returns [rows, N] (N / 2 with the SwiGLU epilogue; rows of unused
     tiles are left as they are), or None when the tcgen05 kernel does not take these sizes."""
@@ -832,7 +869,8 @@ def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, plan: MoEPaddedPlan, 
     _work(f"gemm_tcgen05 grouped{' +swiglu' if swiglu else ''} {used}x{N}x{K}", 2 * (used * K + min(plan.n_experts, plan.n_tiles) * N * K) + used * n_out * out.element_size(),
           2 * used * N * K)
     st = lib().ik_gemm_tcgen05_grouped(_ptr(x), _ptr(w), _ptr(out), _code(out), _ptr(plan.tile_group), plan.n_experts, plan.bn,
-                                       M, N, K, x.stride(0), w.stride(0), out.stride(0), 1 if swiglu else 0, _ptr(status), _stream())
+                                       M, N, K, x.stride(0), w.stride(0), out.stride(0), 1 if swiglu else _act_code(act),
+                                       _ptr(status), _stream())
     if st == -2:
         return None
     _check(st, "gemm_tcgen05_grouped")
@@ -840,8 +878,9 @@ def gemm_tcgen05_grouped(x: torch.Tensor, w: torch.Tensor, plan: MoEPaddedPlan, 
 
 
 def moe_combine(parts: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
-                row_of: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """y[t] = sum_k weight[t, k] * parts[row_of[t * top + k]] (``row_of`` None: row t * top + k)."""
+                row_of: Optional[torch.Tensor] = None, unweighted: bool = False) -> torch.Tensor:
+    """y[t] = sum_k weight[t, k] * parts[row_of[t * top + k]] (``row_of`` None: row t * top + k).  ``unweighted``: a plain sum
+    (``weight`` then only gives the shape)."""
     _need(parts, "parts", torch.float32)
     _need(weight, "weight", torch.float32)
     T, top = weight.shape
@@ -851,7 +890,8 @@ def moe_combine(parts: torch.Tensor, weight: torch.Tensor, out: Optional[torch.T
     if out is None:
         out = torch.empty((T, d), dtype=torch.float32, device=parts.device)
     _work(f"moe_combine {T}x{d}", _nbytes(parts, out))
-    _check(lib().ik_moe_combine(_ptr(parts), _ptr(weight), _ptr(row_of), _ptr(out), T, top, d, _stream()), "moe_combine")
+    _check(lib().ik_moe_combine(_ptr(parts), 0 if unweighted else _ptr(weight), _ptr(row_of), _ptr(out), T, top, d, _stream()),
+           "moe_combine")
     return out
 
 
@@ -1092,8 +1132,10 @@ def norm_rope_append(p: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w: O
                      eps: float, q_out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, token_seq: torch.Tensor,
                      token_pos: torch.Tensor, table: torch.Tensor, inv_freq: Optional[torch.Tensor], magnitude: float,
                      n_heads: int, rotary_dim: int, pairing: int, write_cache: bool, status: Optional[torch.Tensor],
-                     per_head: bool = False) -> None:
-    """RMS norm of q and of k over their whole projections (``q_w``, ``k_w``: weights of that size; None = no norm;
+                     per_head: bool = False, bias: Optional[torch.Tensor] = None, v_norm: bool = False) -> None:
+    """``bias``: a float vector over ``p``'s columns, added to q, k and v as they are read.  ``v_norm``: every value head is
+    divided by the root mean square of its own values (``eps`` inside the root) before it is stored.
+    RMS norm of q and of k over their whole projections (``q_w``, ``k_w``: weights of that size; None = no norm;
     ``per_head``: every head over its own values, with a weight of one head's size that the heads share),
     rotation of each head's leading ``rotary_dim`` dimensions with cos and sin times ``magnitude``, q to ``q_out``,
     k and v into the pages.  q, k, v are column ranges of ``p`` (float)."""
@@ -1108,13 +1150,15 @@ def norm_rope_append(p: torch.Tensor, q_off: int, k_off: int, v_off: int, q_w: O
     if p.stride(1) != 1 or q_out.shape != (T, n_heads * hd) or v_pages.shape[:3] != k_pages.shape[:3] or v_pages.dtype != k_pages.dtype \
             or max(q_off + n_heads * hd, k_off + nkv * hd, v_off + nkv * hdv) > p.shape[1] \
             or (q_w is not None and q_w.numel() != (hd if per_head else n_heads * hd)) \
-            or (k_w is not None and k_w.numel() != (hd if per_head else nkv * hd)):
+            or (k_w is not None and k_w.numel() != (hd if per_head else nkv * hd)) \
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() < max(q_off + n_heads * hd, k_off + nkv * hd, v_off + nkv * hdv))):
         raise KernelError("norm_rope_append: the sizes do not fit together")
     _work(f"norm_rope_append {T}", T * ((n_heads + nkv) * hd + nkv * hdv) * 4 + _nbytes(q_out) + T * nkv * (hd + hdv) * k_pages.element_size())
     _check(lib().ik_norm_rope_append(_ptr(p), p.stride(0), q_off, k_off, v_off, _ptr(q_w), _ptr(k_w), eps, _ptr(q_out), _code(q_out),
                                      _ptr(k_pages), _ptr(v_pages), _code(k_pages), _ptr(token_seq), _ptr(token_pos), _ptr(table),
                                      table.stride(0), _ptr(inv_freq), magnitude, T, n_heads, nkv, hd, hdv, rotary_dim, pairing,
-                                     page_size, n_pages, 1 if write_cache else 0, 1 if per_head else 0, _ptr(status), _stream()), "norm_rope_append")
+                                     page_size, n_pages, 1 if write_cache else 0, 1 if per_head else 0, _ptr(bias), 1 if v_norm else 0, _ptr(status),
+                                     _stream()), "norm_rope_append")
 
 
 def head_gate(att: torch.Tensor, p: Optional[torch.Tensor], g_off: int, out: torch.Tensor, n_heads: int, mult: float = 1.0,
@@ -1184,7 +1228,7 @@ def scale_add_norm(y: torch.Tensor, scale: Optional[torch.Tensor], residual: tor
     return out
 
 
-PLAIN_ACTS = {"relu2": 0, "gelu_tanh": 1}
+PLAIN_ACTS = {"relu2": 0, "gelu_tanh": 1, "tanh": 2}
 
 
 def plain_act(x: torch.Tensor, out_dtype: torch.dtype, act: str) -> torch.Tensor:
@@ -1221,17 +1265,19 @@ def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Ten
 
 # ---------------------------------------------------------------------------------------------
 # The gated delta rule
-def delta_prepare(u: torch.Tensor, q_off: int, k_off: int, p: torch.Tensor, b_off: int, a_off: int, A_log: torch.Tensor,
-                  dt_bias: torch.Tensor, n_qk_heads: int, dk: int, n_heads: int, q_mult: float, unit_eps: float) -> torch.Tensor:
+def delta_prepare(u: torch.Tensor, q_off: int, k_off: int, p: torch.Tensor, b_off: int, a_off: int, A_log: Optional[torch.Tensor],
+                  dt_bias: Optional[torch.Tensor], n_qk_heads: int, dk: int, n_heads: int, q_mult: float, unit_eps: float) -> torch.Tensor:
     """In place: every q and k head of ``u`` (float, behind convolution and activation) becomes a unit vector, q times
-    ``q_mult``.  Returns float [T, 2, heads]: the steps sigmoid(p_b) and the decays exp(-exp(A_log) softplus(p_a + dt_bias))."""
+    ``q_mult``.  Returns float [T, 2, heads]: the steps sigmoid(p_b) and the decays exp(-exp(A_log) softplus(p_a + dt_bias)).
+    ``a_off`` < 0: no decay per head is formed (the second row is not written)."""
     _need(u, "u", torch.float32)
     _need(p, "p", torch.float32, contiguous=False)
-    _need(A_log, "A_log", torch.float32)
-    _need(dt_bias, "dt_bias", torch.float32)
+    if a_off >= 0:
+        _need(A_log, "A_log", torch.float32)
+        _need(dt_bias, "dt_bias", torch.float32)
     T = u.shape[0]
     if p.stride(1) != 1 or max(b_off, a_off) + n_heads > p.shape[1] or max(q_off, k_off) + n_qk_heads * dk > u.shape[1] \
-            or A_log.numel() != n_heads or dt_bias.numel() != n_heads:
+            or (a_off >= 0 and (A_log.numel() != n_heads or dt_bias.numel() != n_heads)):
         raise KernelError("delta_prepare: the sizes do not fit together")
     bg = torch.empty((T, 2, n_heads), dtype=torch.float32, device=u.device)
     _work(f"delta_prepare {T}", 2 * T * 2 * n_qk_heads * dk * 4)
@@ -1264,10 +1310,16 @@ def delta_rule(u: torch.Tensor, q_off: int, k_off: int, v_off: int, bg: torch.Te
 HEAD_GATES = {None: 0, "silu": 1, "sigmoid": 2}
 
 
+def head_norm_gate_into(x: torch.Tensor, weight: torch.Tensor, eps: float, p: Optional[torch.Tensor], g_off: int, n_heads: int,
+                        out: torch.Tensor, gate: Optional[str] = "silu") -> torch.Tensor:
+    """``head_norm_gate`` into a matrix the caller owns (contiguous, [T, heads * dv])."""
+    return head_norm_gate(x, weight, eps, p, g_off, n_heads, out.dtype, gate, out=out)
+
+
 def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, p: Optional[torch.Tensor], g_off: int, n_heads: int,
-                   out_dtype: torch.dtype, gate: Optional[str] = "silu") -> torch.Tensor:
-    """RMS norm of every head of ``x`` [T, heads * dv] over its dv values with one weight of size dv, times
-    silu or sigmoid of columns ``g_off``.. of ``p`` (``gate`` None: no gate)."""
+                   out_dtype: torch.dtype, gate: Optional[str] = "silu", out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMS norm of every head of ``x`` [T, heads * dv] over its dv values with one weight of size dv (or one of size
+    heads * dv: every head its own), times silu or sigmoid of columns ``g_off``.. of ``p`` (``gate`` None: no gate)."""
     _need(x, "x", torch.float32)
     _need(weight, "weight", torch.float32)
     T, cols = x.shape
@@ -1278,12 +1330,17 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, p: Optiona
         if p.stride(1) != 1 or g_off + cols > p.shape[1]:
             raise KernelError("head_norm_gate: the gate has the wrong shape")
         ldp = p.stride(0)
-    if cols % n_heads or weight.numel() != dv:
+    if cols % n_heads or weight.numel() not in (dv, cols):
         raise KernelError("head_norm_gate: the sizes do not fit together")
-    out = torch.empty((T, cols), dtype=out_dtype, device=x.device)
+    if out is None:
+        out = torch.empty((T, cols), dtype=out_dtype, device=x.device)
+    _need(out, "out")
+    if out.shape != (T, cols):
+        raise KernelError("head_norm_gate: the output has the wrong shape")
     _work(f"head_norm_gate {T}x{cols}", T * cols * (8 + out.element_size()))
     _check(lib().ik_head_norm_gate(_ptr(x), _ptr(weight), _ptr(p) if gate is not None else 0, ldp, g_off, _ptr(out), _code(out), T,
-                                   n_heads, dv, eps, HEAD_GATES[gate], _stream()), "head_norm_gate")
+                                   n_heads, dv, eps, HEAD_GATES[gate], dv if (weight.numel() == cols and n_heads > 1) else 0, _stream()),
+           "head_norm_gate")
     return out
 
 
@@ -1291,7 +1348,7 @@ def head_norm_gate(x: torch.Tensor, weight: torch.Tensor, eps: float, p: Optiona
 # Latent attention
 def latent_prepare(p: torch.Tensor, q_off: int, c_off: int, c_w: Optional[torch.Tensor], eps: float, q_plain: torch.Tensor,
                    q_full: torch.Tensor, k_pages: torch.Tensor, token_seq: torch.Tensor, token_pos: torch.Tensor, table: torch.Tensor,
-                   inv_freq: torch.Tensor, n_heads: int, dk: int, dr: int, rank: int, write_cache: bool,
+                   inv_freq: Optional[torch.Tensor], n_heads: int, dk: int, dr: int, rank: int, write_cache: bool,
                    status: Optional[torch.Tensor]) -> None:
     """From the projections ``p`` (float): every query head's plain part to ``q_plain`` [T, heads, dk], its turning part,
     turned, to the last ``dr`` columns of ``q_full`` [T, heads, rank + dr]; when the layer writes rows, the normed latent
@@ -1301,11 +1358,12 @@ def latent_prepare(p: torch.Tensor, q_off: int, c_off: int, c_w: Optional[torch.
     _need(q_full, "q_full", q_plain.dtype)
     _need(k_pages, "k_pages")
     _need(table, "table", torch.int32)
-    _need(inv_freq, "inv_freq", torch.float32)
+    if dr:
+        _need(inv_freq, "inv_freq", torch.float32)
     n_pages, nkv, page_size, hd = k_pages.shape
     T = p.shape[0]
     if p.stride(1) != 1 or nkv != 1 or hd != rank + dr or q_plain.shape != (T, n_heads * dk) or q_full.shape != (T, n_heads * hd) \
-            or inv_freq.numel() != dr // 2 or q_off + n_heads * (dk + dr) > p.shape[1] \
+            or (dr and inv_freq.numel() != dr // 2) or q_off + n_heads * (dk + dr) > p.shape[1] \
             or (write_cache and (c_w is None or c_w.numel() != rank or c_off + hd > p.shape[1])):
         raise KernelError("latent_prepare: the sizes do not fit together")
     _work(f"latent_prepare {T}", T * (n_heads * (dk + dr) * (4 + q_plain.element_size()) + hd * (4 + k_pages.element_size())))
@@ -1313,3 +1371,189 @@ def latent_prepare(p: torch.Tensor, q_off: int, c_off: int, c_w: Optional[torch.
                                    _ptr(k_pages), _code(k_pages), _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0),
                                    _ptr(inv_freq), T, n_heads, dk, dr, rank, page_size, n_pages, 1 if write_cache else 0,
                                    _ptr(status), _stream()), "latent_prepare")
+
+
+def latent_append(p: torch.Tensor, c_off: int, c_w: torch.Tensor, eps: float, k_pages: torch.Tensor, token_seq: torch.Tensor,
+                  token_pos: torch.Tensor, table: torch.Tensor, rank: int, status: Optional[torch.Tensor]) -> None:
+    """The latent alone, for a layer whose queries are made elsewhere and whose rows have no turning part: columns ``c_off``..
+    of ``p`` (float), RMS-normed with ``c_w``, into the token's row of ``k_pages`` [pages, 1, page_size, rank]."""
+    _need(p, "p", torch.float32, contiguous=False)
+    _need(k_pages, "k_pages")
+    _need(table, "table", torch.int32)
+    _need(c_w, "c_w", torch.float32)
+    n_pages, nkv, page_size, hd = k_pages.shape
+    T = p.shape[0]
+    if p.stride(1) != 1 or nkv != 1 or hd != rank or c_w.numel() != rank or c_off + rank > p.shape[1]:
+        raise KernelError("latent_append: the sizes do not fit together")
+    _work(f"latent_append {T}", T * rank * (4 + k_pages.element_size()))
+    _check(lib().ik_latent_prepare(_ptr(p), p.stride(0), 0, c_off, _ptr(c_w), eps, 0, 0, _code(k_pages), _ptr(k_pages), _code(k_pages),
+                                   _ptr(token_seq), _ptr(token_pos), _ptr(table), table.stride(0), 0, T, 0, 0, 0, rank, page_size,
+                                   n_pages, 1, _ptr(status), _stream()), "latent_append")
+
+
+# ---------------------------------------------------------------------------------------------
+# Several residual streams per token; norms that join branches
+def hyper_start(x: torch.Tensor, n: int) -> torch.Tensor:
+    """[T, n, d]: every one of the ``n`` streams a copy of ``x`` [T, d]."""
+    _need(x, "x", torch.float32)
+    T, d = x.shape
+    out = torch.empty((T, n, d), dtype=torch.float32, device=x.device)
+    _work(f"hyper_start {T}x{n}x{d}", _nbytes(x, out))
+    _check(lib().ik_hyper_start(_ptr(x), _ptr(out), T, n, d, _stream()), "hyper_start")
+    return out
+
+
+def hyper_read(xs: torch.Tensor, a: Optional[torch.Tensor], weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+               rows_in: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """rmsnorm(sum_s a[s] xs[:, s, :]) * weight for the rows ``rows_in`` names (all without it); ``a`` None: the plain sum."""
+    _need(xs, "xs", torch.float32)
+    _need(weight, "weight", torch.float32)
+    T, n, d = xs.shape
+    if weight.numel() != d or (a is not None and (a.numel() != n or a.dtype != torch.float32)):
+        raise KernelError("hyper_read: the sizes do not fit together")
+    rows = T if rows_in is None else rows_in.numel()
+    if rows_in is not None:
+        _need(rows_in, "rows_in", torch.int32)
+    out = torch.empty((rows, d), dtype=out_dtype, device=xs.device)
+    _work(f"hyper_read {rows}x{n}x{d}", rows * d * (4 * n + out.element_size()))
+    _check(lib().ik_hyper_read(_ptr(xs), _ptr(rows_in), _ptr(a), _ptr(weight), _ptr(out), _code(out), rows, n, d, eps, _stream()),
+           "hyper_read")
+    return out
+
+
+def hyper_write(xs: torch.Tensor, y: torch.Tensor, mix: torch.Tensor, b: torch.Tensor, a_next: Optional[torch.Tensor] = None,
+                w_next: Optional[torch.Tensor] = None, eps: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """xs[:, k, :] <- sum_s mix[s, k] xs[:, s, :] + b[k] y for all k at once, in place.  With ``a_next`` and ``w_next`` also
+    returns rmsnorm(sum_k a_next[k] xs[:, k, :]) * w_next of the new streams (the next sublayer's operand)."""
+    _need(xs, "xs", torch.float32)
+    _need(y, "y", torch.float32)
+    _need(mix, "mix", torch.float32)
+    _need(b, "b", torch.float32)
+    T, n, d = xs.shape
+    if y.shape != (T, d) or mix.shape != (n, n) or b.numel() != n:
+        raise KernelError("hyper_write: the sizes do not fit together")
+    out = None
+    if a_next is not None:
+        _need(a_next, "a_next", torch.float32)
+        _need(w_next, "w_next", torch.float32)
+        if a_next.numel() != n or w_next.numel() != d:
+            raise KernelError("hyper_write: the next read has the wrong sizes")
+        out = torch.empty((T, d), dtype=out_dtype, device=xs.device)
+    _work(f"hyper_write{' +read' if out is not None else ''} {T}x{n}x{d}", T * d * (8 * n + 4) + _nbytes(out))
+    _check(lib().ik_hyper_write(_ptr(xs), _ptr(y), _ptr(mix), _ptr(b), _ptr(a_next), _ptr(w_next), _ptr(out),
+                                _code(out) if out is not None else F32, T, n, d, eps, _stream()), "hyper_write")
+    return out
+
+
+def branch_norm_sum(ys, biases, weights, scales, out: torch.Tensor, eps: float, accumulate: bool) -> torch.Tensor:
+    """out (+)= sum_b scales[b] * rmsnorm(ys[b] + biases[b]) * weights[b]: up to four float matrices [T, d]; a bias may be None."""
+    n = len(ys)
+    _need(out, "out", torch.float32)
+    T, d = out.shape
+    if not 1 <= n <= 4 or len(biases) != n or len(weights) != n or len(scales) != n:
+        raise KernelError("branch_norm_sum: one to four branches, each with a weight and a constant")
+    for y, bias, w in zip(ys, biases, weights):
+        _need(y, "y", torch.float32)
+        _need(w, "w", torch.float32)
+        if y.shape != (T, d) or w.numel() != d or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != d)):
+            raise KernelError("branch_norm_sum: the sizes do not fit together")
+    arr = ctypes.c_void_p * n
+    cs = (ctypes.c_float * n)(*[float(c) for c in scales])
+    _work(f"branch_norm_sum {n}x{T}x{d}", (n + 1 + (1 if accumulate else 0)) * T * d * 4)
+    _check(lib().ik_branch_norm_sum(arr(*[_ptr(y) for y in ys]), arr(*[_ptr(b) for b in biases]), arr(*[_ptr(w) for w in weights]),
+                                    cs, n, _ptr(out), T, d, eps, 1 if accumulate else 0, _stream()), "branch_norm_sum")
+    return out
+
+
+def add_rows_(y: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """y[t, :] += v for every row of the float matrix ``y`` (a projection's bias)."""
+    _need(y, "y", torch.float32)
+    _need(v, "v", torch.float32)
+    T, d = y.shape
+    if v.numel() != d:
+        raise KernelError("add_rows: the vector does not fit the rows")
+    _work(f"add_rows {T}x{d}", 2 * _nbytes(y))
+    _check(lib().ik_add_rows(_ptr(y), _ptr(v), T, d, _stream()), "add_rows")
+    return y
+
+
+def rmsnorm_range(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm with a weight over ``x`` [rows, d], a column range of a wider float matrix (rows may lie further apart)."""
+    _need(x, "x", torch.float32, contiguous=False)
+    _need(weight, "weight", torch.float32)
+    rows, d = x.shape
+    if x.stride(1) != 1 or weight.numel() != d:
+        raise KernelError("rmsnorm_range: the sizes do not fit together")
+    out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
+    _work(f"rmsnorm_range {rows}x{d}", rows * d * (4 + out.element_size()))
+    _check(lib().ik_rmsnorm_range(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), _code(out), rows, d, eps, _stream()), "rmsnorm_range")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------
+# Recurrences whose state decays row by row
+DECAY_FORMS = {"softplus": 0, "double_exp": 1}
+
+
+def decay_rows(x: torch.Tensor, bias: Optional[torch.Tensor], form: str, A_log: Optional[torch.Tensor] = None,
+               per_head: int = 0) -> torch.Tensor:
+    """Decays in (0, 1) from projections ``x`` [T, C] (float; a column range may be given).  ``softplus``:
+    exp(-exp(A_log[c // per_head]) * softplus(x + bias)); ``double_exp``: exp(-exp(x + bias)).  Formed in double, rounded once."""
+    _need(x, "x", torch.float32, contiguous=False)
+    T, C = x.shape
+    if x.stride(1) != 1 or (bias is not None and (bias.numel() != C or bias.dtype != torch.float32)):
+        raise KernelError("decay_rows: the sizes do not fit together")
+    if form == "softplus" and (A_log is None or per_head <= 0 or A_log.numel() * per_head != C):
+        raise KernelError("decay_rows: the softplus form needs one A_log per head")
+    out = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    _work(f"decay_rows {T}x{C}", 8 * T * C)
+    _check(lib().ik_decay_rows(_ptr(x), x.stride(0), _ptr(bias), _ptr(A_log), _ptr(out), T, C, per_head, DECAY_FORMS[form], _stream()),
+           "decay_rows")
+    return out
+
+
+def token_shift(x: torch.Tensor, mu: torch.Tensor, ring: torch.Tensor, ctx) -> torch.Tensor:
+    """[n_mix, T, d]: x + (x' - x) * mu[m] with x' the input one position earlier in the same sequence (zeros at position
+    0; across steps from ``ring`` [slots, 2, d] float, which then receives every sequence's last input)."""
+    _need(x, "x")
+    _need(mu, "mu", torch.float32)
+    _need(ring, "ring", torch.float32)
+    T, d = x.shape
+    n_mix = mu.shape[0]
+    if mu.shape != (n_mix, d) or tuple(ring.shape[1:]) != (2, d):
+        raise KernelError("token_shift: the sizes do not fit together")
+    out = torch.empty((n_mix, T, d), dtype=x.dtype, device=x.device)
+    _work(f"token_shift {T}x{n_mix}x{d}", (n_mix + 2) * T * d * x.element_size())
+    _check(lib().ik_token_shift(_ptr(x), _code(x), _ptr(mu), _ptr(ring), _ptr(ctx.slots), _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens),
+                                _ptr(ctx.token_seq), _ptr(ctx.token_pos), _ptr(out), T * d, T, ctx.n_seqs, d, n_mix,
+                                1 if ctx.is_decode else 0, _stream()), "token_shift", kernels=1 if ctx.is_decode else 2)
+    return out
+
+
+ROW_RULES = {"delta": 0, "bonus": 1}
+
+
+def row_decay(rule: str, u: torch.Tensor, x1_off: int, k_off: int, v_off: int, dec: torch.Tensor, beta: Optional[torch.Tensor],
+              bonus: Optional[torch.Tensor], state: torch.Tensor, ctx, n_heads: int, n_qk_heads: int, dk: int, dv: int) -> torch.Tensor:
+    """A matrix state per head with a decay per key channel.  ``delta``: S <- diag(a) S; u = beta (v - S^T k); S <- S + k u^T;
+    o = S^T q.  ``bonus``: o = (S + diag(bonus) k v^T)^T r; S <- diag(w) S + k v^T.  q (or r), k and v are column ranges of
+    the float matrix ``u``; ``dec`` [T, heads * dk]; ``beta`` [T, heads] (rows may lie further apart); ``bonus`` [heads * dk]; ``state`` [slots, 2, heads,
+    dv, dk] float.  Returns [T, heads * dv] float."""
+    _need(u, "u", torch.float32, contiguous=False)
+    _need(dec, "dec", torch.float32)
+    _need(state, "state", torch.float32)
+    T = u.shape[0]
+    H, G = n_heads, n_qk_heads
+    if u.stride(1) != 1 or dec.shape != (T, H * dk) or tuple(state.shape[1:]) != (2, H, dv, dk) \
+            or max(x1_off + G * dk, k_off + G * dk, v_off + H * dv) > u.shape[1] \
+            or (rule == "delta" and (beta is None or beta.dtype != torch.float32 or beta.shape != (T, H) or beta.stride(1) != 1)) \
+            or (rule == "bonus" and (bonus is None or bonus.dtype != torch.float32 or bonus.numel() != H * dk)):
+        raise KernelError("row_decay: the sizes do not fit together")
+    out = torch.empty((T, H * dv), dtype=torch.float32, device=u.device)
+    n_state = ctx.n_seqs * H * dk * dv * 4
+    _work(f"row_decay {rule} {T}x{H}x{dk}x{dv}", 2 * n_state + T * (2 * G * dk + H * dk + 2 * H * dv) * 4, 6 * T * H * dk * dv)
+    st = lib().ik_row_decay(ROW_RULES[rule], _ptr(u), u.stride(0), x1_off, k_off, v_off, _ptr(dec), _ptr(beta), beta.stride(0) if beta is not None else 0, _ptr(bonus), _ptr(state),
+                            _ptr(ctx.slots), _ptr(ctx.cu_seqlens), _ptr(ctx.kv_lens), _ptr(out), T, ctx.n_seqs, H, G, dk, dv,
+                            1 if ctx.is_decode else 0, _stream())
+    _check(st, "row_decay")
+    return out

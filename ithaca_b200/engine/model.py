@@ -51,6 +51,10 @@ def streamed_tensor_names(spec: ModelSpec) -> List[str]:
 class DecoderModel:
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         validate_schedule(spec)
+        if spec.streams > 0 and (any(b.kind != "hyper" for b in spec.layers) or any(e.adds_input for e in spec.schedule)):
+            raise ConfigError("a model with residual streams of its blocks' own needs 'hyper' blocks and cannot add its input again")
+        if spec.streams == 0 and any(b.kind == "hyper" for b in spec.layers):
+            raise ConfigError("'hyper' blocks need the model to say how many residual streams there are")
         self.spec = spec
         self.runtime = runtime
         # bytes of the matrices a step streams, in the form the kernels read them: 16-bit on the bfloat16 path
@@ -101,6 +105,8 @@ class DecoderModel:
         h = self.embedding.forward(ctx.token_ids, ctx)
         ctx.shared.pop("stream_copy", None)                    # nothing of an earlier pass over this description counts
         h0 = h.clone() if any(e.adds_input for e in self.spec.schedule) else None
+        if self.spec.streams > 0:
+            h = ops.hyper_start(h, self.spec.streams)          # [T, streams, d]; the final norm reads the streams' sum
         for e in self.spec.schedule:
             if e.adds_input:
                 ops.add_(h, h0)
@@ -129,9 +135,12 @@ def load_model(model_dir: str, runtime: Runtime):
     folder's tensors against what the architecture's parts ask for, and builds the
     model on the runtime's device.  Returns (model, config)."""
     arch, config = config_from_model_dir(model_dir)
+    found = read_model_tensors(model_dir)
+    if hasattr(config, "with_tensor_shapes"):
+        # sizes that the file leaves to the tensors (the rank of a low-rank factor)
+        config = config.with_tensor_shapes({n: tuple(t.shape) for n, t in found.items()})
     spec = config.model_spec()
     manifest = weight_manifest(spec)
-    found = read_model_tensors(model_dir)
     ignore = []
     for name, same_as in spec.aliases.items():
         if name in found and name not in manifest:

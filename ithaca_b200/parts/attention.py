@@ -27,10 +27,13 @@ Options a spec may give (all off by default):
   number per head, a projection of the mixer's input, before the output projection.  ``head_gate: "wide"``: the gate has
   one number per value, ``g`` is [n_heads * v_head_dim, hidden].
 * ``sink``: the softmax's denominator counts one more key of score 0 that carries no value: the weights are
-  exp(s_j) / (1 + sum exp(s_j)), so a query may attend to nothing.
+  exp(s_j) / (1 + sum exp(s_j)), so a query may attend to nothing.  ``sink: "learned"`` with the tensor ``sink`` [n_heads]:
+  every head's sink has a score of its own (not scaled), the denominator's extra term is exp(sink_h).
+* ``bias`` with the tensors ``q_bias``, ``k_bias``, ``v_bias``, ``o_bias``: the four projections add a vector.
+* ``v_norm``: every value head is divided by its root mean square (``norm_eps`` inside the root, no weight) and cached so.
 * a position part whose cos and sin carry a constant factor (``magnitude``).
 
-With one of the last three the mixer runs "wide": one product gives [q | k | v | g] in float, one kernel norms, rotates
+With any of these but the first three the mixer runs "wide": one product gives [q | k | v | g] in float, one kernel norms, rotates
 and appends, the attention kernel runs, and the gate kernel writes the output projection's operand.  A wide mixer can
 also serve as a branch of a composite (``parts/parallel.py``): ``branch_in()`` / ``branch_out()`` hand out its matrices
 so that the composite stacks them with other branches' into one product each, and ``core`` works on column ranges of
@@ -67,6 +70,11 @@ class Attention:
             out[w["k_norm"]] = TensorReq((hd if per_head else nkv * hd,), init="ones")
         if spec.get("head_gate"):
             out[w["g"]] = TensorReq((nh * hdv if spec.get("head_gate") == "wide" else nh, d))
+        if spec.get("sink") == "learned":
+            out[w["sink"]] = TensorReq((nh,), std=1.0)
+        if spec.get("bias"):
+            out[w["q_bias"]], out[w["k_bias"]] = TensorReq((nh * hd,)), TensorReq((nkv * hd,))
+            out[w["v_bias"]], out[w["o_bias"]] = TensorReq((nkv * hdv,)), TensorReq((d,))
         taps = spec.get("conv_taps") or 0
         if taps:
             # taps around 1/taps: the convolution keeps the projections' scale
@@ -104,7 +112,13 @@ class Attention:
         self.head_gate = bool(spec.get("head_gate"))
         self.gate_wide = spec.get("head_gate") == "wide"
         self.sink = bool(spec.get("sink"))
-        self.wide = bool(qk_norm or self.head_gate or self.sink or (position is not None and getattr(position, "magnitude", 1.0) != 1.0)
+        if spec.get("sink") not in (None, False, True, "learned"):
+            raise ValueError(f"attention: sink {spec.get('sink')!r} is not supported (true, learned)")
+        # what the kernels get: False, True (a key of score 0) or every head's score
+        self.sink_arg = as_float32(tensors[w["sink"]], runtime) if spec.get("sink") == "learned" else self.sink
+        self.v_norm = bool(spec.get("v_norm"))
+        self.biased = bool(spec.get("bias"))
+        self.wide = bool(qk_norm or self.head_gate or self.sink or self.v_norm or self.biased or (position is not None and getattr(position, "magnitude", 1.0) != 1.0)
                          or not standalone)
         if self.wide and self.conv_taps:
             raise ValueError("attention: a short convolution and the wide arrangement (qk_norm, head_gate) do not go together")
@@ -132,6 +146,13 @@ class Attention:
         self.g_off = self.v_off + self.n_kv_heads * self.v_head_dim
         self.n_mid = self.n_heads * self.v_head_dim
         self.n_in = self.g_off + ((self.n_mid if self.gate_wide else self.n_heads) if self.head_gate else 0)
+        # the projections' biases as one vector over the columns of the wide product (the gate has none)
+        self.in_bias = None
+        self._out_bias = None
+        if self.biased:
+            zeros = torch.zeros(self.n_in - self.g_off, dtype=torch.float32)
+            self.in_bias = torch.cat([tensors[w[r]].to(torch.float32).cpu() for r in ("q_bias", "k_bias", "v_bias")] + [zeros]).to(runtime.device).contiguous()
+            self._out_bias = as_float32(tensors[w["o_bias"]], runtime)
         if standalone:
             self.qkv = Linear(self._in, runtime)
             self.o = Linear([self._out], runtime)
@@ -153,6 +174,10 @@ class Attention:
         """The matrix that multiplies what ``core`` writes."""
         return self._out
 
+    def branch_out_bias(self):
+        """The vector the output projection adds (float32), or None."""
+        return self._out_bias
+
     def core(self, p: torch.Tensor, mid: torch.Tensor, ctx, cache: LayerCache, writes_cache: bool = True, mult: float = 1.0) -> None:
         """``p`` [T, n_in] float: [q | k | v | g] (a column range of a wider matrix may be given); ``mid`` [T, n_mid] in the
         activation type receives ``mult`` times the gated heads, the operand of the output projection."""
@@ -162,8 +187,8 @@ class Attention:
         ops.norm_rope_append(p, 0, self.k_off, self.v_off, self.q_norm_w, self.k_norm_w, self.norm_eps, q, cache.k_pages,
                              cache.v_pages, ctx.token_seq, ctx.token_pos, table, pos.inv_freq if pos is not None else None,
                              getattr(pos, "magnitude", 1.0), self.n_heads, pos.rotary_dim if pos is not None else 0,
-                             self.pairing, writes_cache, rt.status, per_head=self.norm_per_head)
-        att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt, self.softcap, sink=self.sink)
+                             self.pairing, writes_cache, rt.status, per_head=self.norm_per_head, bias=self.in_bias, v_norm=self.v_norm)
+        att = attend(q, cache, ctx, table, self.n_heads, self.scale, self.window or 0, rt, self.softcap, sink=self.sink_arg)
         ops.head_gate(att, p if self.head_gate else None, self.g_off, mid, self.n_heads, mult, wide=self.gate_wide)
 
     def cache_requests(self) -> List[object]:
@@ -183,6 +208,8 @@ class Attention:
             mid = torch.empty((T, self.n_mid), dtype=rt.act_dtype, device=x.device)
             self.core(p, mid, ctx, cache, writes_cache)
             self.o(mid, out=residual, accumulate=accumulate)
+            if self._out_bias is not None:
+                ops.add_rows_(residual, self._out_bias)
             return
         q = torch.empty((T, self.n_heads * self.head_dim), dtype=rt.act_dtype, device=x.device)
         table = ctx.tables[cache.kv_group]
@@ -213,7 +240,7 @@ class Attention:
 
 
 def attend(q: torch.Tensor, cache: LayerCache, ctx, table: torch.Tensor, n_heads: int, scale: float, window: int,
-           rt: Runtime, softcap: float = 0.0, sink: bool = False) -> torch.Tensor:
+           rt: Runtime, softcap: float = 0.0, sink=False) -> torch.Tensor:
     """Chooses the attention kernel: tensor-core kernels for bfloat16 when they take the
     head sizes, else the CUDA-core kernel (always for float32)."""
     if q.dtype == torch.bfloat16 and cache.v_pages.shape[3] == cache.k_pages.shape[3]:

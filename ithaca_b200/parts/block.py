@@ -17,6 +17,12 @@ behind it scales and adds in one kernel.  The feed-forward may be absent.
 sublayers read the stream itself.  On the 16-bit path their operand is a 16-bit copy of the stream, which the
 norm's kernel writes beside the float stream it adds to (the next sublayer's input, also across layers), so no
 kernel exists only to convert.  The feed-forward may be absent.
+
+``hyper``: n residual streams per token instead of one (the stream tensor is [T, n, d]).  A sublayer f with the layer's
+vectors a, b (size n) and matrix M (n x n, indexed [from, to]) reads u = sum_s a_s x_s through its norm and writes all
+streams at once from the old ones: x_t <- sum_s M[s, t] x_s + b_t f(norm(u)).  The record's parameters name the tensors:
+``{"streams": n, "mixer": {"in": ..., "out": ..., "mix": ...}, "feed_forward": {...}}``.  One kernel reads, one writes;
+the write of the mixer's result already forms the feed-forward's operand from the new streams.  The feed-forward may be absent.
 """
 from __future__ import annotations
 
@@ -232,6 +238,82 @@ class OutNormBlock:
                 ctx.shared[self.COPY] = copy
 
 
+class HyperBlock:
+    ROLES = ("in", "out", "mix")
+
+    @classmethod
+    def manifest(cls, spec: BlockSpec) -> Dict[str, TensorReq]:
+        out: Dict[str, TensorReq] = {}
+        _merge(out, MIXERS.get(spec.mixer.kind).manifest(spec.mixer))
+        if spec.feed_forward is not None:
+            _merge(out, FEED_FORWARDS.get(spec.feed_forward.kind).manifest(spec.feed_forward))
+        for name, n in spec.norms.items():
+            if spec.feed_forward is None and name == "feed_forward":
+                continue
+            _merge(out, NORMS.get(n.kind).manifest(n))
+        if spec.position is not None:
+            _merge(out, POSITIONS.get(spec.position.kind).manifest(spec.position))
+        n = int(spec.params["streams"])
+        for sub in ("mixer",) + (("feed_forward",) if spec.feed_forward is not None else ()):
+            names = spec.params[sub]
+            # random weights: every stream read and written with about equal weight, the streams mostly kept apart
+            _merge(out, {names["in"]: TensorReq((n,), init="ones", std=0.0), names["out"]: TensorReq((n,), init="ones"),
+                         names["mix"]: TensorReq((n, n), std=0.5)})
+        return out
+
+    def __init__(self, spec: BlockSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
+        has_ff = spec.feed_forward is not None
+        self.n = int(spec.params["streams"])
+        if not 1 <= self.n <= 8:
+            raise ValueError(f"hyper block: 1 to 8 streams are supported, found {self.n}")
+        for need in ("mixer",) + (("feed_forward",) if has_ff else ()):
+            if need not in spec.norms or need not in spec.params:
+                raise ValueError(f"hyper block: the spec has no '{need}' norm or stream tensors")
+        position = None
+        if spec.position is not None:
+            position = POSITIONS.get(spec.position.kind)(spec.position, tensors, runtime)
+        mixer_cls = MIXERS.get(spec.mixer.kind)
+        if "position" in inspect.signature(mixer_cls.__init__).parameters:
+            self.mixer = mixer_cls(spec.mixer, tensors, runtime, position=position)
+        else:
+            self.mixer = mixer_cls(spec.mixer, tensors, runtime)
+        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, tensors, runtime) if has_ff else None
+        self.mixer_norm = NORMS.get(spec.norms["mixer"].kind)(spec.norms["mixer"], tensors, runtime)
+        self.ff_norm = NORMS.get(spec.norms["feed_forward"].kind)(spec.norms["feed_forward"], tensors, runtime) if has_ff else None
+        for nm in (self.mixer_norm,) + ((self.ff_norm,) if has_ff else ()):
+            if not (hasattr(nm, "weight") and hasattr(nm, "eps") and not hasattr(nm, "bias")):
+                raise ValueError("hyper block: the norms in front of the sublayers must be RMS norms")
+        self.runtime = runtime
+
+        def stream_tensors(sub):
+            names = spec.params[sub]
+            a, b, m = (as_float32(tensors[names[r]], runtime) for r in self.ROLES)
+            if a.numel() != self.n or b.numel() != self.n or tuple(m.shape) != (self.n, self.n):
+                raise ValueError(f"hyper block: the {sub}'s stream tensors do not fit {self.n} streams")
+            return a, b, m
+
+        self.mixer_in, self.mixer_out, self.mixer_mix = stream_tensors("mixer")
+        if has_ff:
+            self.ff_in, self.ff_out, self.ff_mix = stream_tensors("feed_forward")
+
+    def cache_requests(self) -> List[object]:
+        return list(self.mixer.cache_requests())
+
+    def forward(self, streams: torch.Tensor, ctx, cache: LayerCache, writes_cache: bool = True) -> None:
+        rt = self.runtime
+        T, n, d = streams.shape
+        xn = ops.hyper_read(streams, self.mixer_in, self.mixer_norm.weight, self.mixer_norm.eps, rt.act_dtype)
+        y = torch.empty((T, d), dtype=torch.float32, device=streams.device)
+        self.mixer.forward(xn, ctx, cache, y, writes_cache, accumulate=False)
+        if self.feed_forward is None:
+            ops.hyper_write(streams, y, self.mixer_mix, self.mixer_out)
+            return
+        xn = ops.hyper_write(streams, y, self.mixer_mix, self.mixer_out, self.ff_in, self.ff_norm.weight, self.ff_norm.eps, rt.act_dtype)
+        self.feed_forward.forward(xn, ctx, y, accumulate=False)
+        ops.hyper_write(streams, y, self.ff_mix, self.ff_out)
+
+
 register_block("prenorm", PreNormBlock)
+register_block("hyper", HyperBlock)
 register_block("sandwich", SandwichBlock)
 register_block("outnorm", OutNormBlock)

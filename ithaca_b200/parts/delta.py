@@ -19,6 +19,12 @@ the position the state belongs to, so that a decode step never overwrites what i
 of the last ``conv_taps`` inputs of the convolution, float32.  One product gives [q | k | v | g | b | a] in float; the
 convolution's result, the unit norms, steps, decays, the state and its sums are float32 on both paths; only the
 products' operands are 16-bit on the bfloat16 path.
+
+``decay: "channel"``: one decay per head AND key channel instead of one per head, acting on the rows of S that belong to
+the key channels: g = exp(-exp(A_log_h) * softplus(Wa2 (Wa1 x) + dt_bias)) laid out heads x head_dim, with Wa1 of
+``decay_rank`` rows (tensors ``a1``, ``a2`` instead of ``a``; ``dt_bias`` of size heads * head_dim).  ``gate``: ``silu`` of a
+full projection (``g``), or ``sigmoid_lowrank``: sigmoid(Wg2 (Wg1 x)) with Wg1 of ``gate_rank`` rows (tensors ``g1``, ``g2``).
+The small first factors ride in the one input product; the second factors are products of their own on its columns.
 """
 from __future__ import annotations
 
@@ -44,11 +50,21 @@ class GatedDeltaRule:
         d, H, G, dk, dv, taps = (spec["hidden_size"], spec["n_heads"], spec["n_qk_heads"], spec["head_dim"], spec["v_head_dim"],
                                  spec["conv_taps"])
         w = spec.weights
-        return {w["q"]: TensorReq((G * dk, d)), w["k"]: TensorReq((G * dk, d)), w["v"]: TensorReq((H * dv, d)),
-                w["q_conv"]: TensorReq((G * dk, taps), std=1.0 / taps), w["k_conv"]: TensorReq((G * dk, taps), std=1.0 / taps),
-                w["v_conv"]: TensorReq((H * dv, taps), std=1.0 / taps), w["b"]: TensorReq((H, d)), w["a"]: TensorReq((H, d)),
-                w["A_log"]: TensorReq((H,), std=0.5), w["dt_bias"]: TensorReq((H,), std=0.5),
-                w["norm"]: TensorReq((dv,), init="ones"), w["g"]: TensorReq((H * dv, d)), w["o"]: TensorReq((d, H * dv))}
+        out = {w["q"]: TensorReq((G * dk, d)), w["k"]: TensorReq((G * dk, d)), w["v"]: TensorReq((H * dv, d)),
+               w["q_conv"]: TensorReq((G * dk, taps), std=1.0 / taps), w["k_conv"]: TensorReq((G * dk, taps), std=1.0 / taps),
+               w["v_conv"]: TensorReq((H * dv, taps), std=1.0 / taps), w["b"]: TensorReq((H, d)),
+               w["A_log"]: TensorReq((H,), std=0.5), w["norm"]: TensorReq((dv,), init="ones"), w["o"]: TensorReq((d, H * dv))}
+        if spec.get("decay", "head") == "channel":
+            r = spec["decay_rank"]
+            out.update({w["a1"]: TensorReq((r, d)), w["a2"]: TensorReq((H * dk, r), std=0.2), w["dt_bias"]: TensorReq((H * dk,), std=0.5)})
+        else:
+            out.update({w["a"]: TensorReq((H, d)), w["dt_bias"]: TensorReq((H,), std=0.5)})
+        if spec.get("gate", "silu") == "sigmoid_lowrank":
+            r = spec["gate_rank"]
+            out.update({w["g1"]: TensorReq((r, d)), w["g2"]: TensorReq((H * dv, r), std=0.2)})
+        else:
+            out[w["g"]] = TensorReq((H * dv, d))
+        return out
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         self.hidden = int(spec["hidden_size"])
@@ -67,13 +83,23 @@ class GatedDeltaRule:
             raise ValueError("gated_delta: the convolution needs at least one tap")
         H, G, dk, dv = self.n_heads, self.n_qk_heads, self.head_dim, self.v_head_dim
         w = spec.weights
-        self.in_proj = Linear([tensors[w[r]] for r in ("q", "k", "v", "g", "b", "a")], runtime)
+        decay, gate = spec.get("decay", "head"), spec.get("gate", "silu")
+        if decay not in ("head", "channel") or gate not in ("silu", "sigmoid_lowrank"):
+            raise ValueError(f"gated_delta: decay {decay!r} / gate {gate!r} is not supported (head, channel / silu, sigmoid_lowrank)")
+        self.channel_decay, self.lowrank_gate = decay == "channel", gate == "sigmoid_lowrank"
+        self.decay_rank = int(spec["decay_rank"]) if self.channel_decay else 1
+        self.gate_rank = int(spec["gate_rank"]) if self.lowrank_gate else H * dv
+        # one product: [q | k | v | gate (full, or its first factor) | b | decay (per head, or its first factor)]
+        roles = ["q", "k", "v", "g1" if self.lowrank_gate else "g", "b", "a1" if self.channel_decay else "a"]
+        self.in_proj = Linear([tensors[w[r]] for r in roles], runtime)
+        self.a2 = Linear([tensors[w["a2"]]], runtime) if self.channel_decay else None
+        self.g2 = Linear([tensors[w["g2"]]], runtime) if self.lowrank_gate else None
         self.o = Linear([tensors[w["o"]]], runtime)
         self.k_off = G * dk
         self.v_off = 2 * G * dk
         self.channels = 2 * G * dk + H * dv
         self.g_off = self.channels
-        self.b_off = self.g_off + H * dv
+        self.b_off = self.g_off + self.gate_rank
         self.a_off = self.b_off + H
         cw = torch.cat([tensors[w[r]].to(torch.float32) for r in ("q_conv", "k_conv", "v_conv")], dim=0)
         self.conv_w = cw.to(runtime.device).t().contiguous()                  # tap-major [taps, channels]
@@ -96,10 +122,20 @@ class GatedDeltaRule:
         p = self.in_proj(x, out_dtype=torch.float32)                           # [T, q | k | v | g | b | a]
         ring = cache.state(RING) if self.taps > 1 else None
         u = ops.causal_conv(p[:, :self.channels], self.conv_w, None, ring, ctx, torch.float32, act=True)
-        bg = ops.delta_prepare(u, 0, self.k_off, p, self.b_off, self.a_off, self.A_log, self.dt_bias, G, dk, H, dk ** -0.5,
-                               self.unit_eps)
-        o = ops.delta_rule(u, 0, self.k_off, self.v_off, bg, cache.state(STATE), ctx, H, G, dk, dv)
-        mid = ops.head_norm_gate(o, self.norm_w, self.norm_eps, p, self.g_off, H, rt.act_dtype, gate="silu")
+        if self.channel_decay:
+            bg = ops.delta_prepare(u, 0, self.k_off, p, self.b_off, -1, None, None, G, dk, H, dk ** -0.5, self.unit_eps)
+            low = ops.cast(p[:, self.a_off:self.a_off + self.decay_rank], rt.act_dtype)
+            dec = ops.decay_rows(self.a2(low, out_dtype=torch.float32), self.dt_bias, "softplus", self.A_log, dk)
+            o = ops.row_decay("delta", u, 0, self.k_off, self.v_off, dec, bg[:, 0], None, cache.state(STATE), ctx, H, G, dk, dv)
+        else:
+            bg = ops.delta_prepare(u, 0, self.k_off, p, self.b_off, self.a_off, self.A_log, self.dt_bias, G, dk, H, dk ** -0.5,
+                                   self.unit_eps)
+            o = ops.delta_rule(u, 0, self.k_off, self.v_off, bg, cache.state(STATE), ctx, H, G, dk, dv)
+        if self.lowrank_gate:
+            gate = self.g2(ops.cast(p[:, self.g_off:self.g_off + self.gate_rank], rt.act_dtype), out_dtype=torch.float32)
+            mid = ops.head_norm_gate(o, self.norm_w, self.norm_eps, gate, 0, H, rt.act_dtype, gate="sigmoid")
+        else:
+            mid = ops.head_norm_gate(o, self.norm_w, self.norm_eps, p, self.g_off, H, rt.act_dtype, gate="silu")
         self.o(mid, out=residual, accumulate=accumulate)
 
 

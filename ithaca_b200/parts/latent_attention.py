@@ -15,6 +15,10 @@ space by Wuv (again one small product per head).  Prefill and decode run the sam
 A layer may read the rows that another layer of equal ``kv_rank``, ``rope_dim`` and rotation has written instead of
 making its own (the schedule gives it that layer's cache entry with ``writes_cache=False``): it then has no Wdkv and no
 latent norm, but its own Wuk, Wuv, queries, window and everything else (``own_latent: False``).
+
+``rope_dim: 0``: no turning part at all (no position part is needed; the cached row is the latent alone).  ``q_rank``: the
+queries come through a latent of their own, q = Wuq (rmsnorm(Wdq x) * w) with Wdq of ``q_rank`` rows (tensors ``dq``,
+``dq_norm``, ``uq`` instead of ``q``); it needs ``rope_dim: 0``.
 """
 from __future__ import annotations
 
@@ -38,8 +42,13 @@ class LatentAttention:
         d, H, dk, dr, dv, rank = (spec["hidden_size"], spec["n_heads"], spec["head_dim"], spec["rope_dim"], spec["v_head_dim"],
                                   spec["kv_rank"])
         w = spec.weights
-        out = {w["q"]: TensorReq((H * (dk + dr), d)), w["uk"]: TensorReq((H * dk, rank)), w["uv"]: TensorReq((H * dv, rank)),
-               w["o"]: TensorReq((d, H * dv))}
+        out = {w["uk"]: TensorReq((H * dk, rank)), w["uv"]: TensorReq((H * dv, rank)), w["o"]: TensorReq((d, H * dv))}
+        q_rank = spec.get("q_rank")
+        if q_rank:
+            out.update({w["dq"]: TensorReq((q_rank, d)), w["dq_norm"]: TensorReq((q_rank,), init="ones"),
+                        w["uq"]: TensorReq((H * dk, q_rank), std=q_rank ** -0.5)})
+        else:
+            out[w["q"]] = TensorReq((H * (dk + dr), d))
         if spec.get("own_latent", True):
             out[w["dkv"]] = TensorReq((rank + dr, d))
             out[w["dkv_norm"]] = TensorReq((rank,), init="ones")
@@ -64,17 +73,26 @@ class LatentAttention:
         if gate not in (None, False, "wide"):
             raise ValueError(f"latent_attention: head_gate {gate!r} is not supported (wide)")
         self.gate = bool(gate)
-        if position is None or position.rotary_dim != self.rope_dim or position.pairing != 1 or getattr(position, "magnitude", 1.0) != 1.0:
+        self.q_rank = int(spec.get("q_rank") or 0)
+        if self.rope_dim == 0:
+            position = None
+        elif position is None or position.rotary_dim != self.rope_dim or position.pairing != 1 or getattr(position, "magnitude", 1.0) != 1.0:
             raise ValueError("latent_attention: the turning part needs a rotary position part over all of rope_dim with neighbouring pairs")
+        if self.q_rank and self.rope_dim:
+            raise ValueError("latent_attention: queries through a latent of their own are built for rope_dim 0 only")
         if self.rank > 512:
             raise ValueError(f"latent_attention: the attention kernel keeps up to 512 values of a head's result; kv_rank is {self.rank}")
         self.position = position
         H, dk, dr, dv, rank = self.n_heads, self.head_dim, self.rope_dim, self.v_head_dim, self.rank
         w = spec.weights
-        mats = [tensors[w["q"]]] + ([tensors[w["dkv"]]] if self.own_latent else []) + ([tensors[w["g"]]] if self.gate else [])
+        first = tensors[w["dq"]] if self.q_rank else tensors[w["q"]]
+        mats = [first] + ([tensors[w["dkv"]]] if self.own_latent else []) + ([tensors[w["g"]]] if self.gate else [])
         self.in_proj = Linear(mats, runtime)
         self.o = Linear([tensors[w["o"]]], runtime)
-        self.c_off = H * (dk + dr)
+        if self.q_rank:
+            self.uq = Linear([tensors[w["uq"]]], runtime)
+            self.q_norm_w = as_float32(tensors[w["dq_norm"]], runtime)
+        self.c_off = self.q_rank if self.q_rank else H * (dk + dr)
         self.g_off = self.c_off + (rank + dr if self.own_latent else 0)
         wdt = torch.bfloat16 if runtime.dtype == "bfloat16" else None
         uk = to_device(tensors[w["uk"]], runtime)
@@ -95,12 +113,19 @@ class LatentAttention:
             raise ValueError("latent_attention: a layer without a latent of its own cannot write rows")
         rt, H, dk, dr, dv, rank = self.runtime, self.n_heads, self.head_dim, self.rope_dim, self.v_head_dim, self.rank
         T, hd = x.shape[0], rank + dr
-        p = self.in_proj(x, out_dtype=torch.float32)                       # [T, q | (c, key part) | g]
-        q_plain = torch.empty((T, H * dk), dtype=rt.act_dtype, device=x.device)
+        p = self.in_proj(x, out_dtype=torch.float32)                       # [T, q (or its latent) | (c, key part) | g]
         q_full = torch.empty((T, H * hd), dtype=rt.act_dtype, device=x.device)
         table = ctx.tables[cache.kv_group]
-        ops.latent_prepare(p, 0, self.c_off, self.c_norm_w, self.norm_eps, q_plain, q_full, cache.k_pages, ctx.token_seq,
-                           ctx.token_pos, table, self.position.inv_freq, H, dk, dr, rank, writes_cache, rt.status)
+        if self.q_rank:
+            cq = ops.rmsnorm_range(p[:, :self.q_rank], self.q_norm_w, self.norm_eps, rt.act_dtype)
+            q_plain = self.uq(cq, out_dtype=rt.act_dtype)
+            if writes_cache:
+                ops.latent_append(p, self.c_off, self.c_norm_w, self.norm_eps, cache.k_pages, ctx.token_seq, ctx.token_pos, table,
+                                  rank, rt.status)
+        else:
+            q_plain = torch.empty((T, H * dk), dtype=rt.act_dtype, device=x.device)
+            ops.latent_prepare(p, 0, self.c_off, self.c_norm_w, self.norm_eps, q_plain, q_full, cache.k_pages, ctx.token_seq,
+                               ctx.token_pos, table, self.position.inv_freq if dr else None, H, dk, dr, rank, writes_cache, rt.status)
         ops.gemm_heads(q_plain.view(T, H, dk), self.uk_t, q_full.view(T, H, hd)[:, :, :rank])
         # [T, H * rank]: the tensor-core kernel whose tile rows are the heads, or (32-bit, other sizes) the CUDA cores
         att = attention_latent.attend(q_full, cache.k_pages, ctx, table, H, self.scale, self.window or 0, rt.status, rank)

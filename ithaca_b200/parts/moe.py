@@ -1,10 +1,14 @@
-"""Mixture of experts: a router and small gated feed-forwards, of which each token uses a few.
+"""Mixture of experts: a router and small feed-forwards, of which each token uses a few.
 
 Router: z = Wr x in float32 (x may be the activations' 16-bit rounding), scores = softmax(z)
-over all experts.  Experts may form equal groups of neighbours: a group counts by its best
+over all experts (``score: "sigmoid"``: the sigmoid of every logit by itself).  Experts may form equal groups of neighbours: a group counts by its best
 score, and only experts of the ``group_keep`` best groups can be chosen.  The ``top`` best of
 them are; their weights are their scores (``renormalize``: divided by their sum).  An expert is
 y = Wd (silu(Wg x) * (Wu x)); the layer's output is the weighted sum of the chosen experts'.
+
+``expert: "plain"``: an expert is ungated, y = Wd act(Wu x) with ``activation`` ``relu2`` or ``gelu_tanh`` (no ``gate`` tensors).
+``weight_on: "input"``: the weight multiplies what the expert reads instead of what it gives, y = sum_e expert_e(w_e x); the
+scaled rows are formed (in float, rounded once to the operands' type) while the tokens are gathered into expert order.
 
 On the device: one kernel forms the router's logits and picks experts and weights per token; a counting sort groups the
 (token, choice) pairs by expert; two grouped products run every expert over its rows (the first
@@ -39,7 +43,8 @@ class MoEFeedForward:
         """The spec names the router's tensor and a pattern per expert matrix with ``{e}`` for the expert."""
         w = spec.weights
         E = int(spec["n_experts"])
-        return w["router"], [(w["gate"].format(e=e), w["up"].format(e=e), w["down"].format(e=e)) for e in range(E)]
+        gated = spec.get("expert", "gated") != "plain"
+        return w["router"], [(w["gate"].format(e=e) if gated else None, w["up"].format(e=e), w["down"].format(e=e)) for e in range(E)]
 
     @classmethod
     def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
@@ -47,13 +52,31 @@ class MoEFeedForward:
         router, experts = cls._roles(spec)
         out = {router: TensorReq((spec["n_experts"], d), std=2.0 / d ** 0.5)}       # random weights: logits a few units apart
         for g, u, dn in experts:
-            out[g], out[u], out[dn] = TensorReq((ff, d)), TensorReq((ff, d)), TensorReq((d, ff))
+            out[u], out[dn] = TensorReq((ff, d)), TensorReq((d, ff))
+            if g is not None:
+                out[g] = TensorReq((ff, d))
         return out
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
-        act = spec.get("activation", "silu")
-        if act != "silu":
-            raise ValueError(f"moe: activation {act!r} is not supported (silu)")
+        kind = spec.get("expert", "gated")
+        if kind not in ("gated", "plain"):
+            raise ValueError(f"moe: expert {kind!r} is not supported (gated, plain)")
+        self.gated = kind == "gated"
+        act = spec.get("activation", "silu" if self.gated else "relu2")
+        if self.gated and act != "silu":
+            raise ValueError(f"moe: activation {act!r} is not supported by gated experts (silu)")
+        if not self.gated and act not in ops.PLAIN_ACTS:
+            raise ValueError(f"moe: activation {act!r} is not supported by plain experts ({', '.join(ops.PLAIN_ACTS)})")
+        self.act = act
+        self.score = spec.get("score", "softmax")
+        if self.score not in ops.MOE_SCORES:
+            raise ValueError(f"moe: score {self.score!r} is not supported ({', '.join(ops.MOE_SCORES)})")
+        where = spec.get("weight_on", "output")
+        if where not in ("output", "input"):
+            raise ValueError(f"moe: weight_on {where!r} is not supported (output, input)")
+        self.weight_on_input = where == "input"
+        if self.weight_on_input and self.gated:
+            raise ValueError("moe: weights on the experts' input are built for plain experts only")
         self.hidden = int(spec["hidden_size"])
         self.intermediate = int(spec["intermediate_size"])
         self.n_experts = int(spec["n_experts"])
@@ -79,8 +102,11 @@ class MoEFeedForward:
             return (t.to(wt) if wt is not None else t).contiguous()
 
         # gate j and up j in rows 2j and 2j + 1, so that a product tile holds both halves of every pair it covers
-        self.gate_up = stack([torch.stack((tensors[g], tensors[u]), dim=1).reshape(2 * self.intermediate, self.hidden)
-                              for g, u, _ in experts])                                                 # [E, 2 ff, d]
+        if self.gated:
+            self.gate_up = stack([torch.stack((tensors[g], tensors[u]), dim=1).reshape(2 * self.intermediate, self.hidden)
+                                  for g, u, _ in experts])                                             # [E, 2 ff, d]
+        else:
+            self.up = stack([tensors[u] for _, u, _ in experts])                                       # [E, ff, d]
         self.down = stack([tensors[dn] for _, _, dn in experts])                                       # [E, d, ff]
         self.runtime = runtime
         self.tensor_cores = runtime.dtype == "bfloat16" and self.hidden % 8 == 0 and self.intermediate % 8 == 0
@@ -92,29 +118,36 @@ class MoEFeedForward:
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor, accumulate: bool = True) -> None:
         rt = self.runtime
-        routed = ops.moe_router(x, self.router, self.top, self.n_groups, self.group_keep, self.renormalize)
+        routed = ops.moe_router(x, self.router, self.top, self.n_groups, self.group_keep, self.renormalize, self.score)
         if routed is None:                                   # sizes beyond the fused kernel's shared memory
             logits = ops.gemm_simt(x, self.router, out_dtype=torch.float32)
-            routed = ops.moe_route(logits, self.top, self.n_groups, self.group_keep, self.renormalize)
+            routed = ops.moe_route(logits, self.top, self.n_groups, self.group_keep, self.renormalize, self.score)
         chosen, weight = routed
         parts = row_of = None
+        on_input = self.weight_on_input
         if self.tensor_cores:
             plan = ops.moe_sort_padded(chosen, self.n_experts, self.tile_rows(x.shape[0]))
-            xp = ops.moe_gather(x, plan)
+            xp = ops.moe_gather(x, plan, weight if on_input else None)
             E, ff, d = self.n_experts, self.intermediate, self.hidden
-            h = ops.gemm_tcgen05_grouped(xp, self.gate_up.view(E * 2 * ff, d), plan, torch.bfloat16, swiglu=True, status=rt.status)
+            if self.gated:
+                h = ops.gemm_tcgen05_grouped(xp, self.gate_up.view(E * 2 * ff, d), plan, torch.bfloat16, swiglu=True, status=rt.status)
+            else:
+                h = ops.gemm_tcgen05_grouped(xp, self.up.view(E * ff, d), plan, torch.bfloat16, status=rt.status, act=self.act)
             if h is not None:
                 parts = ops.gemm_tcgen05_grouped(h, self.down.view(E * d, ff), plan, torch.float32, status=rt.status)
                 row_of = plan.row_of
         if parts is None:
             plan = ops.moe_sort(chosen, self.n_experts)
-            h = ops.moe_gemm(0, x, self.gate_up, plan, rt.act_dtype)
+            if self.gated:
+                h = ops.moe_gemm(0, x, self.gate_up, plan, rt.act_dtype)
+            else:
+                h = ops.moe_gemm(2, x, self.up, plan, rt.act_dtype, row_scale=weight if on_input else None, act=self.act)
             parts = ops.moe_gemm(1, h, self.down, plan, torch.float32)
             row_of = None
         if accumulate:
-            ops.add_(residual, ops.moe_combine(parts, weight, row_of=row_of))
+            ops.add_(residual, ops.moe_combine(parts, weight, row_of=row_of, unweighted=on_input))
         else:
-            ops.moe_combine(parts, weight, out=residual, row_of=row_of)
+            ops.moe_combine(parts, weight, out=residual, row_of=row_of, unweighted=on_input)
 
 
 register_feed_forward("moe", MoEFeedForward)

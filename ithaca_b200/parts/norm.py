@@ -4,7 +4,8 @@
 Layer norm: y = (x - mean) / sqrt(var + eps) * w + b with var the mean of the squared
 deviations, in float32.  A norm may also stand behind a sublayer: ``add_into`` then adds
 ``mult * y`` to the residual stream in the same kernel.  The RMS norm may carry a second vector
-(``scale``, a per-channel "layer scale") that multiplies what it adds to the stream."""
+(``scale``, a per-channel "layer scale") that multiplies what it adds to the stream.  With ``scalar_weight`` the RMS
+norm's weight is ONE number for all coordinates (stored as a tensor without dimensions); the kernels get it spread out."""
 from __future__ import annotations
 
 from typing import Dict, Mapping, Optional
@@ -20,7 +21,7 @@ from .base import Runtime, as_float32, register_norm
 class RMSNorm:
     @classmethod
     def manifest(cls, spec: PartSpec) -> Dict[str, TensorReq]:
-        out = {spec.weights["weight"]: TensorReq((spec["size"],), init="ones")}
+        out = {spec.weights["weight"]: TensorReq(() if spec.get("scalar_weight") else (spec["size"],), init="ones")}
         if "scale" in spec.weights:
             out[spec.weights["scale"]] = TensorReq((spec["size"],), init="ones")
         return out
@@ -29,11 +30,15 @@ class RMSNorm:
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.weight = as_float32(tensors[spec.weights["weight"]], runtime)
+        if spec.get("scalar_weight"):
+            self.weight = self.weight.reshape(1).expand(self.size).contiguous()
         self.scale = as_float32(tensors[spec.weights["scale"]], runtime) if "scale" in spec.weights else None
         self.runtime = runtime
 
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None,
                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        if x.dim() == 3:                  # several streams per token [T, n, d]: the norm of their plain sum
+            return ops.hyper_read(x, None, self.weight, self.eps, out_dtype or self.runtime.act_dtype, rows_in=rows)
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype or self.runtime.act_dtype, rows_in=rows)
 
     def add_into(self, x: torch.Tensor, residual: torch.Tensor, mult: float = 1.0, copy: Optional[torch.Tensor] = None) -> None:
