@@ -116,7 +116,7 @@ def write_file(path: str, tensors: Dict[str, torch.Tensor], metadata: Dict[str, 
         f.write(struct.pack("<Q", len(raw)))
         f.write(raw)
         for name in order:
-            t = tensors[name].detach().contiguous().cpu()
+            t = tensors[name].detach().contiguous().cpu().reshape(-1)        # (a tensor without dimensions has one element)
             f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
 
 

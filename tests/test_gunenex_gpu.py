@@ -1,0 +1,914 @@
+"""The Gunenex decoder and its mechanisms against the plain implementation (tests/plain/gunenex_plain.py).
+
+Small configurations with weights made here.  Per mechanism: the kernel against the plain function, also across several
+steps where it carries a state, and a one-layer model of each mixer and feed-forward.  Whole models: prompts against
+token-by-token decoding, portions down to two tokens, batches of unequal requests against each alone, slots, pages and
+states that are used again, long decoding, and greedy generation through the engine's own loop.  Where random weights would
+hide a fault (a far key, a sink, a state or a shifted input that was lost on the way), the weights are made so that one
+token decides the result.
+"""
+import copy
+import json
+import os
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import REL, random_ids, rel_err, run_schedule
+from plain import gunenex_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _left(heads, kv, dim, vdim, scale, rot=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale}
+    if rot is not None:
+        m["rot"] = {"dims": rot[0], "base": rot[1]}
+    return m
+
+
+def _par(left, heads, dim, rank=None):
+    right = {"heads": heads, "dim": dim}
+    if rank is not None:
+        right["rank"] = rank
+    return {"left": left, "right": right}
+
+
+def _lat(heads, dim, vdim, rank, q_rank, scale, kv_from=None):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "kv_rank": rank, "q_rank": q_rank, "scale": scale}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _delta(heads, kv, dim, vdim, conv, decay_rank=None, gate_rank=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "conv": conv}
+    if decay_rank is not None:
+        m["decay_rank"] = decay_rank
+    if gate_rank is not None:
+        m["gate_rank"] = gate_rank
+    return m
+
+
+def _ff(n):
+    return None if n is None else {"kind": "dense", "ff": n}
+
+
+def _moe(ff, experts, top):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+# unlike layers in an unusual order: a latent layer first, read again three layers later by a layer with other heads and sizes;
+# part of the head turned and none; key sizes unlike value sizes; grouped and ungrouped heads in both recurrent mixers; ranks
+# that are no multiple of eight; layers without feed-forward; two and one expert a token
+CFG_A = {
+    "architecture": "Gunenex", "vocab": 101, "width": 64, "streams": 3, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "latent_attention", "mixer": _lat(3, 16, 24, 40, 24, 0.2), "mlp": _moe(24, 5, 2)},
+        {"type": "parallel", "mixer": _par(_left(4, 2, 32, 16, 0.2, rot=(16, 500.0)), 2, 24, rank=12), "mlp": _ff(88)},
+        {"type": "channel_delta", "mixer": _delta(4, 2, 24, 40, 3, decay_rank=12, gate_rank=20), "mlp": None},
+        {"type": "latent_attention", "mixer": _lat(2, 8, 16, 40, 16, 0.3, kv_from=0), "mlp": _ff(40)},
+        {"type": "parallel", "mixer": _par(_left(2, 2, 16, 16, 0.3), 3, 16), "mlp": _moe(40, 6, 1)},
+        {"type": "channel_delta", "mixer": _delta(3, 3, 80, 16, 1), "mlp": _ff(56)},
+    ],
+}
+# one head, one stream and one expert everywhere; every expert chosen; four taps; sizes the tensor-core kernels take (attention
+# heads of 64, a latent of 64, the whole head turned)
+CFG_B = {
+    "architecture": "Gunenex", "vocab": 67, "width": 48, "streams": 1, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "parallel", "mixer": _par(_left(1, 1, 64, 64, 0.15, rot=(64, 10000.0)), 1, 32), "mlp": _moe(32, 1, 1)},
+        {"type": "channel_delta", "mixer": _delta(1, 1, 16, 32, 4), "mlp": _moe(16, 3, 3)},
+        {"type": "latent_attention", "mixer": _lat(1, 32, 8, 64, 8, 0.25), "mlp": None},
+    ],
+}
+# eight streams; a latent wide enough for the kernel whose tile rows are the heads, read by a layer with forty heads; attention
+# heads of 128 in groups of four; recurrent states of 128 rows
+CFG_C = {
+    "architecture": "Gunenex", "vocab": 89, "width": 64, "streams": 8, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "latent_attention", "mixer": _lat(5, 16, 24, 128, 32, 0.2), "mlp": _ff(72)},
+        {"type": "latent_attention", "mixer": _lat(40, 8, 8, 128, 8, 0.3, kv_from=0), "mlp": None},
+        {"type": "parallel", "mixer": _par(_left(8, 2, 128, 128, 0.09, rot=(64, 250000.0)), 1, 128), "mlp": _moe(48, 8, 3)},
+        {"type": "channel_delta", "mixer": _delta(2, 1, 128, 32, 2), "mlp": _ff(48)},
+    ],
+}
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+
+
+def make_tensors(cfg, seed):
+    """Weights by name with the shapes the library asks for; scales chosen so that activations are of order one."""
+    from ithaca_b200.config import config_from_dict
+    from ithaca_b200.engine.model import weight_manifest
+    g = torch.Generator().manual_seed(seed)
+    n = cfg["streams"]
+    out = {}
+    for name, req in weight_manifest(config_from_dict(cfg)[1].model_spec()).items():
+        shape = tuple(req.shape)
+        r = torch.randn(shape, generator=g)
+        last = name.rsplit(".", 1)[-1]
+        if name == "embed":
+            t = r
+        elif ".hc" in name:
+            t = {"in": 1.0 / n + 0.3 * r, "out": 0.8 + 0.3 * r, "mix": torch.eye(n) * 0.8 + 0.25 * r}[last]
+        elif ".mu." in name:
+            t = torch.rand(shape, generator=g)
+        elif "norm" in name or last == "out":
+            t = 1.0 + 0.1 * r
+        elif last == "conv":
+            t = 0.6 * r
+        elif last in ("dt_bias", "w0"):
+            t = 0.5 * r - 1.0
+        elif last == "A_log":
+            t = 0.5 * r - 0.5
+        elif last in ("sink", "u"):
+            t = 0.7 * r
+        elif last == "b" and len(shape) == 1:
+            t = 0.3 * r
+        elif last == "router":
+            t = r * (3.0 / shape[1] ** 0.5)
+        else:
+            t = r * (1.2 / shape[1] ** 0.5)
+        out[name] = t.bfloat16()
+    return out
+
+
+def _write(tmp, cfg, tensors, tag):
+    from ithaca_b200.weights.safetensors_io import write_file
+    d = os.path.join(str(tmp), tag)
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_file(os.path.join(d, "model.safetensors"), tensors, {"format": "pt"})
+    return d
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gunenex")
+    out = {}
+    for i, (n, c) in enumerate(CONFIGS.items()):
+        t = make_tensors(c, 70 + i)
+        out[n] = (_write(root, c, t, n), t)
+    return out
+
+
+def _close(got, want, dtype):
+    """float32: every logit within the tolerance.  bfloat16: the median row must hold the tolerance and four rows in five two
+    and a half times it.  The rest are tokens whose router met a close call: with 16-bit operands the logits of two experts a
+    few hundredths apart change places, the token then runs through another expert than in the plain implementation, and
+    its row (and, more faintly, what later tokens read of it) differs by tenths.  A wrong key or a lost state moves every
+    row behind it by tens of hundredths: see the needle tests, which have no router and hold every row to the tolerance."""
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape and np.all(np.isfinite(got))
+    rows = np.abs(got - want).reshape(-1, want.shape[-1]).max(-1) / max(np.abs(want).max(), 1e-30)
+    if dtype == "float32":
+        return bool(rows.max() < REL[dtype])
+    return bool(np.median(rows) < REL[dtype] and np.quantile(rows, 0.8) < 2.5 * REL[dtype])
+
+
+def _plain(cfg, t, ids):
+    return P.forward(cfg, t, ids).numpy()
+
+
+def _ctx(lo, hi, slots):
+    """The device arrays of a step in which sequence b brings positions lo[b] .. hi[b] - 1."""
+    new = [h - l for l, h in zip(lo, hi)]
+    i32 = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    return SimpleNamespace(
+        n_seqs=len(lo), is_decode=all(n == 1 for n in new), slots=i32(slots), cu_seqlens=i32(np.concatenate([[0], np.cumsum(new)])),
+        kv_lens=i32(hi), token_seq=i32(np.repeat(np.arange(len(lo)), new)),
+        token_pos=i32(np.concatenate([np.arange(l, h) for l, h in zip(lo, hi)]) if sum(new) else []))
+
+
+# a prompt, a portion behind it, then single tokens, for three sequences of which one has a single token at first
+STEPS = [([0, 0, 0], [67, 1, 60]), ([67, 1, 60], [70, 2, 131]), ([70, 2, 131], [71, 3, 132]), ([71, 3, 132], [72, 4, 133])]
+TOTAL = [72, 4, 133]
+SLOTS = [4, 0, 2]
+
+
+# ------------------------------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("n,d", [(1, 48), (3, 256), (4, 1100), (8, 72)])
+def test_stream_kernels(n, d):
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(n * d)
+    T = 9
+    x = torch.randn(T, d, generator=g)
+    xs = ops.hyper_start(x.to(DEV), n)
+    assert xs.shape == (T, n, d) and all(torch.equal(xs[:, s].cpu(), x) for s in range(n))
+    xs = torch.randn(T, n, d, generator=g)
+    a, b, a2 = torch.randn(n, generator=g), torch.randn(n, generator=g), torch.randn(n, generator=g)
+    M = torch.randn(n, n, generator=g)
+    w, w2 = torch.randn(d, generator=g), torch.randn(d, generator=g)
+    y = torch.randn(T, d, generator=g) * 2
+    u = torch.einsum("s,tsd->td", a.double(), xs.double())
+    got = ops.hyper_read(xs.to(DEV), a.to(DEV), w.to(DEV), 1e-5, torch.float32)
+    assert rel_err(got.cpu().numpy(), (P.rms(u, 1e-5) * w.double()).numpy()) < 3e-6
+    rows = torch.tensor([7, 0, 3], dtype=torch.int32)
+    got = ops.hyper_read(xs.to(DEV), None, w.to(DEV), 1e-5, torch.float32, rows_in=rows.to(DEV))
+    assert rel_err(got.cpu().numpy(), (P.rms(xs.double().sum(1), 1e-5) * w.double())[rows.long()].numpy()) < 3e-6
+    new = torch.einsum("sk,tsd->tkd", M.double(), xs.double()) + b.double()[None, :, None] * y.double()[:, None, :]
+    dev = xs.clone().to(DEV)
+    assert ops.hyper_write(dev, y.to(DEV), M.to(DEV), b.to(DEV)) is None
+    assert rel_err(dev.cpu().numpy(), new.numpy()) < 3e-6
+    for dt, tol in ((torch.float32, 3e-6), (torch.bfloat16, 8e-3)):
+        dev2 = xs.clone().to(DEV)
+        nxt = ops.hyper_write(dev2, y.to(DEV), M.to(DEV), b.to(DEV), a2.to(DEV), w2.to(DEV), 1e-5, dt)
+        assert torch.equal(dev2, dev)
+        want = P.rms(torch.einsum("k,tkd->td", a2.double(), new), 1e-5) * w2.double()
+        assert rel_err(nxt.float().cpu().numpy(), want.numpy()) < tol
+
+
+def test_branch_norm_sum_and_range_norm():
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(4)
+    T, d = 11, 200
+    ys = [torch.randn(T, d, generator=g) * s for s in (1.0, 30.0, 0.01)]
+    bs = [torch.randn(d, generator=g), None, torch.randn(d, generator=g) * 0.01]
+    ws = [torch.randn(d, generator=g) for _ in range(3)]
+    cs = [0.5, 0.5, -2.0]
+    want = sum(c * P.rms(y.double() + (0 if b is None else b.double()), 1e-5) * w.double() for y, b, w, c in zip(ys, bs, ws, cs))
+    base = torch.randn(T, d, generator=g)
+    for n in (1, 2, 3):
+        w_n = sum(c * P.rms(y.double() + (0 if b is None else b.double()), 1e-5) * w.double() for y, b, w, c in list(zip(ys, bs, ws, cs))[:n])
+        dev = lambda seq: [None if v is None else v.to(DEV) for v in seq[:n]]
+        out = base.clone().to(DEV)
+        ops.branch_norm_sum(dev(ys), dev(bs), dev(ws), cs[:n], out, 1e-5, False)
+        assert rel_err(out.cpu().numpy(), w_n.numpy()) < 3e-6
+        out = base.clone().to(DEV)
+        ops.branch_norm_sum(dev(ys), dev(bs), dev(ws), cs[:n], out, 1e-5, True)
+        assert rel_err(out.cpu().numpy(), (base.double() + w_n).numpy()) < 3e-6
+    assert rel_err(want.numpy(), w_n.numpy()) == 0.0
+    wide = torch.randn(T, 300, generator=g)
+    got = ops.rmsnorm_range(wide.to(DEV)[:, 37:237], ws[0].to(DEV), 1e-6, torch.float32)
+    assert rel_err(got.cpu().numpy(), (P.rms(wide[:, 37:237].double(), 1e-6) * ws[0].double()).numpy()) < 3e-6
+    y = base.clone().to(DEV)
+    ops.add_rows_(y, ws[1].to(DEV))
+    assert rel_err(y.cpu().numpy(), (base + ws[1]).numpy()) < 1e-7
+
+
+def test_decay_forms():
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(6)
+    T, H, dk = 13, 3, 20
+    x = torch.randn(T, 5 + H * dk, generator=g) * 3
+    bias, A = torch.randn(H * dk, generator=g), torch.randn(H, generator=g)
+    z = x[:, 5:].double() + bias.double()
+    got = ops.decay_rows(x.to(DEV)[:, 5:], bias.to(DEV), "softplus", A.to(DEV), dk)
+    want = torch.exp(-torch.exp(A.double()).repeat_interleave(dk) * P.softplus(z))
+    assert rel_err(got.cpu().numpy(), want.numpy()) < 2e-7
+    got = ops.decay_rows(x.to(DEV)[:, 5:], bias.to(DEV), "double_exp")
+    assert rel_err(got.cpu().numpy(), torch.exp(-torch.exp(z)).numpy()) < 2e-7
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_token_shift_across_steps(dtype):
+    """Five mixes of every token with the one before it in its own sequence: within a step, across steps through the ring
+    (slots in another order than the sequences, leftovers in the ring), zeros at position 0."""
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(8)
+    d, n_mix = 72, 5
+    xs = [torch.randn(n, d, generator=g).to(dtype) for n in TOTAL]
+    mu = torch.rand(n_mix, d, generator=g)
+    ring = torch.randn(6, 2, d, generator=g).to(DEV)                          # leftovers: a sequence at position 0 must not see them
+    for lo, hi in STEPS:
+        x = torch.cat([xs[b][l:h] for b, (l, h) in enumerate(zip(lo, hi))])
+        got = ops.token_shift(x.to(DEV), mu.to(DEV), ring, _ctx(lo, hi, SLOTS))
+        want = []
+        for b, (l, h) in enumerate(zip(lo, hi)):
+            cur = xs[b][l:h].double()
+            prev = torch.cat([torch.zeros(1, d, dtype=torch.float64) if l == 0 else xs[b][l - 1:l].double(), cur[:-1]])
+            want.append(cur[None] + (prev - cur)[None] * mu.double()[:, None, :])
+        want = torch.cat(want, dim=1)
+        assert rel_err(got.float().cpu().numpy(), want.numpy()) < (1e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("rule", ["delta", "bonus"])
+@pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 24, 40), (3, 3, 80, 16), (1, 1, 16, 32), (2, 1, 128, 128), (2, 2, 200, 8), (6, 6, 48, 48)])
+def test_row_decay_kernels(rule, H, G, dk, dv):
+    """Both rules with a decay per key channel across four steps of three sequences (a prompt, a portion, two single
+    tokens), leftovers in the states, q, k and v as column ranges of a wider matrix."""
+    from ithaca_b200.csrc import ops
+    if rule == "bonus":
+        G = H
+    g = torch.Generator().manual_seed(H * dk + dv)
+    pad = 4
+    width = pad + 2 * G * dk + H * dv + 3
+    us = [torch.randn(n, width, generator=g) * 0.5 for n in TOTAL]
+    if rule == "delta":                       # unit keys, as the mixer makes them: the rule is a contraction only then
+        for u in us:
+            for hd in range(2 * G):
+                part = u[:, pad + hd * dk:pad + (hd + 1) * dk]
+                part /= part.norm(dim=1, keepdim=True)
+    decs = [torch.rand(n, H * dk, generator=g) * 0.5 + 0.5 for n in TOTAL]
+    betas = [torch.rand(n, 2, H, generator=g) for n in TOTAL]
+    bonus = torch.randn(H * dk, generator=g)
+    state = torch.randn(6, 2, H, dv, dk, generator=g).to(DEV)
+    outs = [[] for _ in TOTAL]
+    for lo, hi in STEPS:
+        cat = lambda seqs: torch.cat([s[l:h] for s, l, h in zip(seqs, lo, hi)]).to(DEV)
+        bg = cat(betas)
+        o = ops.row_decay(rule, cat(us)[:, pad:], 0, G * dk, 2 * G * dk, cat(decs), bg[:, 0] if rule == "delta" else None,
+                          bonus.to(DEV) if rule == "bonus" else None, state, _ctx(lo, hi, SLOTS), H, G, dk, dv)
+        off = 0
+        for b, (l, h) in enumerate(zip(lo, hi)):
+            outs[b].append(o[off:off + h - l].cpu())
+            off += h - l
+    for b, n in enumerate(TOTAL):
+        u = us[b][:, pad:].double()
+        q, k = u[:, :G * dk].reshape(n, G, dk), u[:, G * dk:2 * G * dk].reshape(n, G, dk)
+        v = u[:, 2 * G * dk:2 * G * dk + H * dv].reshape(n, H, dv)
+        a = decs[b].double().reshape(n, H, dk)
+        if rule == "delta":
+            q, k = q.repeat_interleave(H // G, dim=1), k.repeat_interleave(H // G, dim=1)
+            want = P.channel_delta_rule(q, k, v, betas[b][:, 0].double(), a)
+        else:
+            want = torch.zeros(n, H, dv, dtype=torch.float64)
+            for h in range(H):
+                S = torch.zeros(dk, dv, dtype=torch.float64)
+                for i in range(n):
+                    kv = torch.outer(k[i, h], v[i, h])
+                    want[i, h] = (S + bonus.double()[h * dk:(h + 1) * dk, None] * kv).T @ q[i, h]
+                    S = a[i, h][:, None] * S + kv
+        assert rel_err(torch.cat(outs[b]).numpy(), want.reshape(n, -1).numpy()) < 2e-5, b
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,hdv,rot", [(6, 2, 16, 8, 8), (2, 2, 32, 32, 32), (3, 1, 24, 40, 0), (9, 9, 40, 8, 12)])
+def test_biases_and_value_norm_in_the_append_kernel(dtype, nh, nkv, hd, hdv, rot):
+    from test_kernels_gpu import Paged
+    from ithaca_b200.csrc import ops
+    lens, new = [70, 5, 130], [3, 5, 66]
+    T, pad = sum(new), 7
+    g = torch.Generator().manual_seed(hd + rot)
+    n_in = (nh + nkv) * hd + nkv * hdv
+    wide = torch.randn(T, pad + n_in + 3, generator=g)
+    bias = torch.randn(n_in + 3, generator=g)
+    pk, pv = Paged(lens, nkv, hd, dtype, 5), Paged(lens, nkv, hdv, dtype, 5)
+    k_d, v_d, tab = pk.dev()[0], pv.dev()[0], pk.dev()[2]
+    seq = torch.from_numpy(np.repeat(np.arange(3), new).astype(np.int32)).to(DEV)
+    posn = np.concatenate([np.arange(l - n, l) for l, n in zip(lens, new)])
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    freqs = torch.tensor([300.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32, device=DEV) if rot else None
+    ops.norm_rope_append(wide.to(DEV)[:, pad:], 0, nh * hd, (nh + nkv) * hd, None, None, 1e-5, q_out, k_d, v_d, seq,
+                         torch.from_numpy(posn.astype(np.int32)).to(DEV), tab, freqs, 1.0, nh, rot, 0, True, status,
+                         bias=bias.to(DEV), v_norm=True)
+    assert status.item() == 0
+    x = wide[:, pad:pad + n_in].double() + bias[:n_in].double()
+    q, k = x[:, :nh * hd].reshape(T, nh, hd), x[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd)
+    v = P.rms(x[:, (nh + nkv) * hd:].reshape(T, nkv, hdv), 1e-5)
+    if rot:
+        q, k = P.rotate_halves(q, posn, rot, 300.0), P.rotate_halves(k, posn, rot, 300.0)
+    tol = 5e-6 if dtype == torch.float32 else 8e-3
+    assert rel_err(q_out.float().cpu().numpy(), q.reshape(T, -1).numpy()) < tol
+    t = 0
+    for b, (l, n) in enumerate(zip(lens, new)):
+        for j in range(l - n, l):
+            kk, vv = k_d.cpu()[pk.table[b, j // 64], :, j % 64].float(), v_d.cpu()[pk.table[b, j // 64], :, j % 64].float()
+            assert rel_err(kk.numpy(), k[t].numpy()) < tol and rel_err(vv.numpy(), v[t].numpy()) < tol
+            t += 1
+
+
+def _sink_case(nh, nkv, hd, hdv, dtype):
+    from test_kernels_gpu import Paged
+    lens = [1, 70, 200, 129, 64, 700]
+    g = torch.Generator().manual_seed(hd + nh)
+    ks = [torch.randn(l, nkv, hd, generator=g) for l in lens]
+    vs = [torch.randn(l, nkv, hdv, generator=g) for l in lens]
+    # small and large queries: the sink takes most of the weight for some and next to none for others
+    qs = [torch.randn(l, nh, hd, generator=g) * torch.linspace(0.05, 3.0, l)[:, None, None] for l in lens]
+    sink = torch.linspace(-3.0, 4.0, nh)
+    pk, pv = Paged(lens, nkv, hd, dtype, 3), Paged(lens, nkv, hdv, dtype, 3)
+    pk.fill(ks, ks)
+    pv.fill(vs, vs)
+    rt = lambda a: a.to(dtype).double()
+    full = [P.causal_attention(rt(qs[b]), rt(ks[b]), rt(vs[b]), 0.3, sink.double()) for b in range(len(lens))]
+    zero = [P.causal_attention(rt(qs[b]), rt(ks[b]), rt(vs[b]), 0.3, torch.zeros(nh, dtype=torch.float64)) for b in range(len(lens))]
+    return lens, qs, sink, pk, pv, full, zero
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,hdv", [(4, 2, 16, 8), (3, 1, 48, 24), (2, 2, 64, 64)])
+def test_a_learned_sink_in_the_cuda_core_attention(dtype, nh, nkv, hd, hdv):
+    from ithaca_b200.csrc import ops
+    lens, qs, sink, pk, pv, full, zero = _sink_case(nh, nkv, hd, hdv, dtype)
+    k_d, v_d, tab = pk.dev()[0], pv.dev()[0], pk.dev()[2]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for new in ([1, 70, 67, 129, 5, 40], [1] * len(lens)):
+        seq = torch.from_numpy(np.repeat(np.arange(len(lens)), new).astype(np.int32)).to(DEV)
+        posn = torch.from_numpy(np.concatenate([np.arange(l - n, l) for l, n in zip(lens, new)]).astype(np.int32)).to(DEV)
+        q = torch.cat([a[l - n:] for a, l, n in zip(qs, lens, new)]).reshape(sum(new), nh * hd).to(dtype).to(DEV)
+        want = torch.cat([a[l - n:] for a, l, n in zip(full, lens, new)]).reshape(sum(new), -1).numpy()
+        other = torch.cat([a[l - n:] for a, l, n in zip(zero, lens, new)]).reshape(sum(new), -1).numpy()
+        assert rel_err(other, want) > 0.1                                        # the sink's own score matters here
+        out = ops.attention_simt(q, k_d, v_d, seq, posn, tab, nh, 0.3, 0, status, sink=sink.to(DEV))
+        assert status.item() == 0
+        assert rel_err(out.float().cpu().numpy(), want) < (5e-6 if dtype == torch.float32 else 8e-3)
+        out = ops.attention_simt(q, k_d, v_d, seq, posn, tab, nh, 0.3, 0, status, sink=True)
+        assert rel_err(out.float().cpu().numpy(), other) < (5e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("nh,nkv,hd,kind", [(4, 2, 16, "mma"), (2, 2, 32, "mma"), (4, 2, 64, "tc"), (8, 2, 128, "tc"), (2, 1, 128, "mma"),
+                                            (3, 3, 64, "tc")])
+def test_a_learned_sink_in_the_tensor_core_attention(nh, nkv, hd, kind):
+    """Prompts' portions (both kernels) and single tokens (chunks of one and of four pages): the sink joins the running
+    maximum and sum once, with its head's own score, however many pages and chunks a query's keys span."""
+    from ithaca_b200.csrc import attention_bf16 as A
+    i32 = lambda a: torch.from_numpy(np.asarray(a, dtype=np.int32)).to(DEV)
+    lens, qs, sink, pk, pv, full, zero = _sink_case(nh, nkv, hd, hd, torch.bfloat16)
+    k_d, v_d, tab = pk.dev()[0], pv.dev()[0], pk.dev()[2]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for new in ([1, 70, 67, 129, 5, 450], [1] * len(lens)):
+        q = torch.cat([a[l - n:] for a, l, n in zip(qs, lens, new)]).reshape(sum(new), nh * hd).bfloat16().to(DEV)
+        want = torch.cat([a[l - n:] for a, l, n in zip(full, lens, new)]).reshape(sum(new), -1).numpy()
+        other = torch.cat([a[l - n:] for a, l, n in zip(zero, lens, new)]).reshape(sum(new), -1).numpy()
+        assert rel_err(other, want) > 0.1
+        if max(new) > 1:
+            got = [A.prefill(q, k_d, v_d, i32(np.concatenate([[0], np.cumsum(new)])), i32(lens), tab, len(lens), max(new), nh, 0.3,
+                             0, status, kind=kind, sink=sink.to(DEV))]
+        else:
+            got = [A.decode(q, k_d, v_d, i32(lens), tab, len(lens), max(lens), nh, 0.3, 0, status, chunk_pages=c, sink=sink.to(DEV))
+                   for c in (1, 4)]
+        assert status.item() == 0
+        for o in got:
+            assert rel_err(o.float().cpu().numpy(), want) < 8e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_head_norm_with_a_weight_per_head(dtype):
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(2)
+    T, H, dv = 9, 5, 24
+    x, gate = torch.randn(T, H * dv, generator=g) * 4, torch.randn(T, 3 + H * dv, generator=g)
+    w = torch.randn(H * dv, generator=g)
+    got = ops.head_norm_gate(x.to(DEV), w.to(DEV), 1e-5, gate.to(DEV), 3, H, dtype, gate="silu")
+    want = P.rms(x.double().reshape(T, H, dv), 1e-5).reshape(T, -1) * w.double() * P.silu(gate[:, 3:].double())
+    assert rel_err(got.float().cpu().numpy(), want.numpy()) < (3e-6 if dtype == torch.float32 else 8e-3)
+    own = torch.empty(T, H * dv, dtype=dtype, device=DEV)
+    ops.head_norm_gate_into(x.to(DEV), w.to(DEV), 1e-5, gate.to(DEV), 3, H, own, gate="sigmoid")
+    want = P.rms(x.double().reshape(T, H, dv), 1e-5).reshape(T, -1) * w.double() * P.sigmoid(gate[:, 3:].double())
+    assert rel_err(own.float().cpu().numpy(), want.numpy()) < (3e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("E,top", [(5, 2), (16, 1), (3, 3), (40, 4)])
+def test_sigmoid_routing(E, top):
+    from ithaca_b200.csrc import ops
+    g = torch.Generator().manual_seed(E)
+    T, K = 70, 64
+    x, wr = torch.randn(T, K, generator=g), torch.randn(E, K, generator=g) * 0.3
+    s = P.sigmoid(x.double() @ wr.double().T)
+    order = torch.argsort(-s, dim=1, stable=True)[:, :top]
+    for routed in (ops.moe_router(x.to(DEV), wr.to(DEV), top, score="sigmoid"),
+                   ops.moe_route((x @ wr.T).to(DEV), top, score="sigmoid")):
+        chosen, weight = routed
+        assert torch.equal(chosen.cpu().long(), order)
+        assert rel_err(weight.cpu().numpy(), torch.gather(s, 1, order).numpy()) < 2e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d,ff,E,top", [(64, 24, 5, 2), (48, 40, 1, 1), (128, 96, 16, 1), (72, 16, 3, 3)])
+def test_plain_experts_with_weights_on_their_input(dtype, d, ff, E, top):
+    """The routed feed-forward as a part: sigmoid scores, no renormalising, ungated experts with the square of relu, each
+    reading its score times the token.  Prompts and single tokens (other tile heights of the grouped product)."""
+    from ithaca_b200.config.spec import PartSpec
+    from ithaca_b200.parts import FEED_FORWARDS, Runtime
+    g = torch.Generator().manual_seed(d + E)
+    t = {"p.router": (torch.randn(E, d, generator=g) * (0.7 / d ** 0.5)).bfloat16()}     # logits of order one: no sigmoid rounds to 1
+    for e in range(E):
+        t[f"p.e{e}.up"] = (torch.randn(ff, d, generator=g) / d ** 0.5).bfloat16()
+        t[f"p.e{e}.down"] = (torch.randn(d, ff, generator=g) / ff ** 0.5).bfloat16()
+    spec = PartSpec("moe", {"hidden_size": d, "intermediate_size": ff, "n_experts": E, "top": top, "score": "sigmoid", "expert": "plain",
+                            "activation": "relu2", "weight_on": "input"},
+                    {"router": "p.router", "up": "p.e{e}.up", "down": "p.e{e}.down"})
+    rt = Runtime(dtype=dtype, device=DEV)
+    part = FEED_FORWARDS.get("moe")(spec, t, rt)
+    for T in (1, 3, 150):
+        x = (torch.randn(T, d, generator=g) * 2).to(rt.act_dtype)
+        res = torch.full((T, d), 7.0, device=DEV)
+        part.forward(x.to(DEV), None, res, accumulate=False)
+        want = P.routed_feed_forward(x.double(), {"router": {"top": top}}, {k: v.double() for k, v in t.items()}, "p")
+        assert rel_err(res.cpu().numpy(), want.numpy()) < (1e-5 if dtype == "float32" else 2.5e-2), T
+        part.forward(x.to(DEV), None, res, accumulate=True)
+        assert rel_err(res.cpu().numpy(), 2 * want.numpy()) < (1e-5 if dtype == "float32" else 2.5e-2), T
+
+
+# ------------------------------------------------------------------------------------------ one layer of each kind
+def _one_layer(kind, mixer, width=48, mlp=None, streams=2):
+    return {"architecture": "Gunenex", "vocab": 53, "width": width, "streams": streams, "norm": {"eps": 1e-5},
+            "layers": [{"type": kind, "mixer": mixer, "mlp": mlp}]}
+
+
+ONE_LAYER = {
+    "parallel": _one_layer("parallel", _par(_left(4, 2, 16, 24, 0.25, rot=(8, 100.0)), 2, 16)),
+    "parallel, heads of their own, nothing turned": _one_layer("parallel", _par(_left(3, 3, 8, 8, 0.4), 1, 8, rank=5), mlp=_ff(32)),
+    "parallel, tensor-core sizes": _one_layer("parallel", _par(_left(4, 1, 64, 64, 0.12, rot=(64, 10000.0)), 3, 64), width=64),
+    "delta": _one_layer("channel_delta", _delta(4, 2, 16, 24, 4)),
+    "delta, one tap": _one_layer("channel_delta", _delta(2, 2, 48, 8, 1, decay_rank=3, gate_rank=40), mlp=_ff(40)),
+    "latent": _one_layer("latent_attention", _lat(3, 16, 24, 32, 16, 0.2)),
+    "latent, a wide one": _one_layer("latent_attention", _lat(5, 16, 24, 64, 24, 0.2), streams=5),
+    "routed": _one_layer("latent_attention", _lat(2, 24, 8, 20, 12, 0.3), mlp=_moe(24, 7, 2), streams=1),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(ONE_LAYER))
+def test_one_layer_models(tmp_path, name, dtype):
+    from ithaca_b200 import Engine
+    cfg = ONE_LAYER[name]
+    t = make_tensors(cfg, 11)
+    eng = Engine(_write(tmp_path, cfg, t, "one"), dtype=dtype, max_tokens=1024)
+    reqs = {"a": random_ids(150, 53, 1), "b": random_ids(9, 53, 2)}
+    want = {r: _plain(cfg, t, ids) for r, ids in reqs.items()}
+    got = run_schedule(eng, reqs, [[("a", 150), ("b", 9)]])
+    assert all(_close(got[r], want[r], dtype) for r in reqs)
+    got = run_schedule(eng, reqs, [[("a", 70), ("b", 2)], [("a", 3), ("b", 1)]] + [[("a", 1), ("b", 1)]] * 6 + [[("a", 71)]])
+    assert all(_close(got[r], want[r], dtype) for r in reqs)
+
+
+# ------------------------------------------------------------------------------------------ whole models
+SCHEDULES = {
+    "token by token": lambda n: [[("a", 1)] for _ in range(n)],
+    "portions of two": lambda n: [[("a", 2)] for _ in range(n // 2)] + ([[("a", n % 2)]] if n % 2 else []),
+    "portions of three and seven": lambda n: _portions(n, [3, 7]),
+    "portions of 64 and 65": lambda n: _portions(n, [64, 65]),
+    "prompt then decode": lambda n: [[("a", n - 81)]] + [[("a", 1)] for _ in range(81)],
+}
+
+
+def _portions(n, sizes):
+    out, i = [], 0
+    while n > 0:
+        k = min(n, sizes[i % len(sizes)])
+        out.append([("a", k)])
+        n -= k
+        i += 1
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompts(models, name, dtype):
+    from ithaca_b200 import Engine
+    d, t = models[name]
+    eng = Engine(d, dtype=dtype, max_tokens=2048)
+    for n in (1, 2, 63, 64, 65, 200):
+        ids = random_ids(n, CONFIGS[name]["vocab"], n)
+        assert _close(run_schedule(eng, {"a": ids}, [[("a", n)]])["a"], _plain(CONFIGS[name], t, ids), dtype), n
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sched", list(SCHEDULES))
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_the_same_logits_however_a_prompt_is_cut(models, name, sched, dtype):
+    from ithaca_b200 import Engine
+    d, t = models[name]
+    n = 150
+    ids = random_ids(n, CONFIGS[name]["vocab"], 7)
+    eng = Engine(d, dtype=dtype, max_tokens=1024)
+    got = run_schedule(eng, {"a": ids}, SCHEDULES[sched](n))["a"]
+    assert _close(got, _plain(CONFIGS[name], t, ids), dtype)
+    if dtype == "float32":
+        whole = run_schedule(eng, {"a": ids}, [[("a", n)]])["a"]
+        assert np.abs(got - whole).max() <= 2e-6 * np.abs(whole).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_unequal_batches_against_each_request_alone(models, name, dtype):
+    """Requests of 1 to 200 tokens start together and are decoded together; the short ones end earlier.  Then portions of
+    some beside single tokens of others."""
+    from ithaca_b200 import Engine
+    d, t = models[name]
+    V = CONFIGS[name]["vocab"]
+    reqs = {r: random_ids(n, V, 40 + n) for r, n in (("a", 1), ("b", 66), ("c", 200), ("d", 13), ("e", 130))}
+    want = {r: _plain(CONFIGS[name], t, ids) for r, ids in reqs.items()}
+    eng = Engine(d, dtype=dtype, max_tokens=2048)
+    first = {"a": 1, "b": 60, "c": 190, "d": 9, "e": 126}
+    sched = [[(r, first[r]) for r in reqs]]
+    left = {r: len(reqs[r]) - first[r] for r in reqs}
+    while any(left.values()):
+        sched.append([(r, 1) for r in reqs if left[r] > 0])
+        left = {r: max(0, n - 1) for r, n in left.items()}
+    got = run_schedule(eng, reqs, sched)
+    assert all(_close(got[r], want[r], dtype) for r in reqs)
+    mixed = [[("c", 64), ("b", 1)], [("c", 65), ("b", 2), ("e", 7)], [("b", 63), ("c", 1), ("e", 1)], [("c", 70), ("e", 122)]]
+    got = run_schedule(eng, {r: reqs[r] for r in "bce"}, mixed)
+    assert all(_close(got[r], want[r], dtype) for r in "bce")
+    if dtype == "float32":
+        alone = run_schedule(eng, {"c": reqs["c"]}, [[("c", 200)]])["c"]
+        assert np.abs(got["c"] - alone).max() <= 2e-6 * np.abs(alone).max()
+
+
+def test_slots_pages_and_states_are_used_again(models):
+    """A small cache: requests come and go, so slots, pages, states, rings and last inputs are handed out again, also to
+    shorter sequences whose first tokens must see nothing of what lay there before."""
+    from ithaca_b200 import Engine
+    d, t = models["A"]
+    eng = Engine(d, dtype="float32", max_tokens=64 * 6, max_slots=2)
+    for round_ in range(4):
+        reqs = {"x": random_ids(170 - 50 * round_, 101, 20 + round_), "y": random_ids(3 + round_, 101, 30 + round_)}
+        got = run_schedule(eng, reqs, [[("x", len(reqs["x"]) - 2), ("y", 2)], [("x", 1), ("y", 1)], [("x", 1)]]
+                           + [[("y", 1)] for _ in range(round_)])
+        for r, ids in reqs.items():
+            assert rel_err(got[r], _plain(CFG_A, t, ids)) < REL["float32"], (round_, r)
+        eng.cache.table.check_consistent()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(models, dtype):
+    from ithaca_b200 import Engine
+    d, t = models["A"]
+    ids = random_ids(330, 101, 77)
+    want = _plain(CFG_A, t, ids)
+    eng = Engine(d, dtype=dtype, max_tokens=1024)
+    got = run_schedule(eng, {"a": ids}, [[("a", 10)]] + [[("a", 1)] for _ in range(320)])["a"]
+    assert _close(got, want, dtype)
+
+
+def test_other_sizes_than_multiples_of_eight(tmp_path):
+    """A width, ranks and head sizes that no tensor-core kernel takes: the CUDA-core kernels serve both number types."""
+    from ithaca_b200 import Engine
+    cfg = {"architecture": "Gunenex", "vocab": 37, "width": 30, "streams": 2, "norm": {"eps": 1e-5}, "layers": [
+        {"type": "parallel", "mixer": _par(_left(3, 1, 10, 6, 0.3, rot=(6, 77.0)), 2, 5, rank=3), "mlp": _moe(7, 4, 2)},
+        {"type": "latent_attention", "mixer": _lat(2, 6, 10, 18, 7, 0.4), "mlp": _ff(21)},
+        {"type": "channel_delta", "mixer": _delta(2, 1, 5, 7, 2, decay_rank=2, gate_rank=3), "mlp": None}]}
+    t = make_tensors(cfg, 3)
+    d = _write(tmp_path, cfg, t, "odd")
+    ids = random_ids(90, 37, 8)
+    want = _plain(cfg, t, ids)
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine(d, dtype=dtype, max_tokens=512)
+        got = run_schedule(eng, {"a": ids}, [[("a", 66)], [("a", 3)]] + [[("a", 1)]] * 21)["a"]
+        assert _close(got, want, dtype)
+
+
+# ------------------------------------------------------------------------------------------ one token decides
+D = 32
+
+
+def _needle_base(cfg):
+    """Token 1 (the needle) and token 2 (the query) point along axis 0, every other token along an axis of its own; the
+    needle carries a mark on axis 5.  One stream that the sublayer writes into with a weight of three."""
+    t = make_tensors(cfg, 9)
+    g = torch.Generator().manual_seed(1)
+    emb = torch.randn(40, D, generator=g) * 0.05
+    for i in range(3, 40):
+        emb[i, 8 + i % 20] += 4.0
+    emb[1] += torch.eye(D)[0] * 4 + torch.eye(D)[5] * 2
+    emb[2] += torch.eye(D)[0] * 4 - torch.eye(D)[5] * 2
+    t["embed"] = emb.bfloat16()
+    one = lambda v: torch.tensor(v).bfloat16()
+    t["l0.norm1"] = t["final.norm"] = one(1.0)
+    t["l0.hc1.in"], t["l0.hc1.mix"] = one([1.0]), one([[1.0]])
+    t["l0.hc1.out"] = one([3.0])                                       # what the mixer adds outweighs the token's own embedding
+    return t
+
+
+def _needle_latent():
+    """The down-projection copies the input into the latent, Wuk and Wuv copy the latent, the query's two factors copy the
+    input with the mark's axis turned over: the query's best match is the needle, ahead of itself and of hundreds of others;
+    the value it fetches carries the needle's mark."""
+    cfg = _one_layer("latent_attention", _lat(1, D, D, D, D, 1.2), width=D, streams=1)
+    cfg["vocab"] = 40
+    t = _needle_base(cfg)
+    flip = torch.eye(D)
+    flip[5, 5] = -1.0
+    t["l0.mix.dq"], t["l0.mix.uq"] = torch.eye(D).bfloat16(), flip.bfloat16()
+    t["l0.mix.dkv"] = t["l0.mix.uk"] = t["l0.mix.uv"] = t["l0.mix.o"] = torch.eye(D).bfloat16()
+    t["l0.mix.dq.norm"] = t["l0.mix.dkv.norm"] = torch.ones(D).bfloat16()
+    return cfg, t
+
+
+def _needle_parallel(which):
+    """A parallel layer of which one branch does the work and the other adds nothing that moves (zero output matrix: its
+    normed result is zero).  ``left``: the attention finds the needle among hundreds of keys.  ``right``: the time mixing
+    hardly forgets (decays next to one); only the needle has a key that the query's receptance meets."""
+    cfg = _one_layer("parallel", _par(_left(1, 1, D, D, 1.2), 1, D), width=D, streams=1)
+    cfg["vocab"] = 40
+    t = _needle_base(cfg)
+    eye, flip = torch.eye(D), torch.eye(D)
+    flip[5, 5] = -1.0
+    for r in "qkvo":
+        t[f"l0.mix.left.{r}.b"] = torch.zeros_like(t[f"l0.mix.left.{r}.b"])
+    t["l0.mix.left.q"], t["l0.mix.left.k"], t["l0.mix.left.v"] = flip.bfloat16(), eye.bfloat16(), eye.bfloat16()
+    t["l0.mix.left.g"] = torch.zeros(1, D).bfloat16()
+    t["l0.mix.left.sink"] = torch.zeros(1).bfloat16()
+    t["l0.mix.left.o"] = (eye if which == "left" else torch.zeros(D, D)).bfloat16()
+    t["l0.mix.left.out"] = t["l0.mix.right.out"] = torch.ones(D).bfloat16()
+    for s in "rkvgw":
+        t[f"l0.mix.right.mu.{s}"] = torch.zeros(D).bfloat16()           # no shift: every projection reads the token itself
+    pick = torch.zeros(D, D)
+    pick[0, 0] = 1.0
+    t["l0.mix.right.r"] = t["l0.mix.right.k"] = pick.bfloat16()         # receptance and key: axis 0 only
+    mark = torch.zeros(D, D)
+    mark[5, 5] = 1.0
+    t["l0.mix.right.v"] = mark.bfloat16()                               # the value carries the mark alone
+    t["l0.mix.right.g"] = (4 * eye).bfloat16()
+    t["l0.mix.right.w1"] = torch.zeros_like(t["l0.mix.right.w1"])
+    t["l0.mix.right.w0"] = torch.full((D,), -12.0).bfloat16()           # decay exp(-exp(-12)): next to one
+    t["l0.mix.right.u"] = torch.zeros(1, D).bfloat16()                  # no bonus: the query reads the state alone
+    t["l0.mix.right.norm"] = torch.ones(D).bfloat16()
+    t["l0.mix.right.o"] = (eye if which == "right" else torch.zeros(D, D)).bfloat16()
+    t["embed"][3:, 0] = 0.0                                             # the others' keys are exactly zero: they write nothing
+    return cfg, t
+
+
+def _needle_delta():
+    """A delta rule that hardly forgets (decays next to one on every key channel): only the needle and the query have a key,
+    along axis 0, and only the needle writes firmly, so what the query reads from the state is the needle's value, however
+    long ago it was written."""
+    cfg = _one_layer("channel_delta", _delta(1, 1, D, D, 2, decay_rank=8, gate_rank=D), width=D, streams=1)
+    cfg["vocab"] = 40
+    t = _needle_base(cfg)
+    pick = torch.zeros(D, D)
+    pick[0, 0] = 2.0                                                    # q and k: axis 0 only; silu(0) = 0 elsewhere
+    t["l0.mix.q"] = t["l0.mix.k"] = pick.bfloat16()
+    mark = torch.eye(D)
+    mark[5, 5] = 3.0
+    t["l0.mix.v"], t["l0.mix.o"] = mark.bfloat16(), torch.eye(D).bfloat16()
+    last = torch.zeros(D, 2)
+    last[:, 1] = 1.0                                                    # the convolution passes the current token through
+    for r in "qkv":
+        t[f"l0.mix.{r}.conv"] = last.bfloat16()
+    gate = 4 * torch.eye(D)
+    gate[5, 5] = -4.0                                                   # the query's gate is open where the needle's mark arrives
+    t["l0.mix.g1"], t["l0.mix.g2"] = torch.eye(D).bfloat16(), gate.bfloat16()
+    t["l0.mix.norm"] = torch.ones(D).bfloat16()
+    t["l0.mix.b"] = torch.zeros(1, D).bfloat16()
+    t["l0.mix.b"][0, 5] = 2.0                                           # the mark decides the step: the needle writes firmly
+    t["embed"][3:, 0] = 0.0
+    t["l0.mix.a1"] = torch.zeros_like(t["l0.mix.a1"])
+    t["l0.mix.dt_bias"] = torch.full((D,), -6.0).bfloat16()
+    t["l0.mix.A_log"] = torch.zeros(1).bfloat16()
+    return cfg, t
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("make", [_needle_latent, lambda: _needle_parallel("left"), lambda: _needle_parallel("right"), _needle_delta],
+                         ids=["latent", "attention", "time mixing", "delta"])
+def test_the_one_early_token_that_matters(tmp_path, make, dtype):
+    """The needle sits at the very start, at a page's last and first place and elsewhere far back; the query comes at the
+    end of a prompt, is decoded alone after it, or follows a short portion; a batch neighbour runs beside it."""
+    from ithaca_b200 import Engine
+    cfg, t = make()
+    d = _write(tmp_path, cfg, t, "needle")
+    eng = Engine(d, dtype=dtype, max_tokens=4096)
+    n = 400
+    hay = [3 + (i * 7) % 37 for i in range(n)]
+    tol = REL[dtype] if dtype == "float32" else 6e-2
+    none = list(hay)
+    none[n - 1] = 2
+    base = _plain(cfg, t, none)[n - 1]
+    for at in (0, 1, 63, 64, 127, 128, 300):
+        ids = list(hay)
+        ids[at], ids[n - 1] = 1, 2
+        want = _plain(cfg, t, ids)[n - 1]
+        assert rel_err(want, base) > 0.15, at                              # the test has teeth: without the needle, other logits
+        for cut in (n, n - 1, n - 5, 65):
+            s, other = eng.alloc_slot(), eng.alloc_slot()
+            lg = eng.step([other, s], [hay[:7], ids[:cut]], "last")
+            for x in ids[cut:]:
+                lg = eng.step([s, other], [[x], [5]], "last")
+            eng.free_slot(s)
+            eng.free_slot(other)
+            row = lg.cpu().numpy()[1 if cut == n else 0]
+            assert rel_err(row, want) < tol, (at, cut)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_token_before_decides(tmp_path, dtype):
+    """Every projection of the time mixing reads the token BEFORE (mu = 1): a token's logits depend on its predecessor alone,
+    within a portion, across portions, when decoded one by one, and in a slot that was used before; the first token reads
+    zeros."""
+    from ithaca_b200 import Engine
+    cfg, t = _needle_parallel("right")
+    for s in "rkvgw":
+        t[f"l0.mix.right.mu.{s}"] = torch.ones(D).bfloat16()
+    t["l0.mix.right.u"] = torch.ones(1, D).bfloat16()                      # the bonus lets a token read its own (shifted) write
+    t["embed"][3:, 0] = 0.3
+    d = _write(tmp_path, cfg, t, "shift")
+    eng = Engine(d, dtype=dtype, max_tokens=1024, max_slots=2)
+    ids = [1, 2, 2, 1, 7, 2, 1] + [3 + (i * 5) % 30 for i in range(60)] + [1, 2, 9, 1]
+    want = _plain(cfg, t, ids)
+    other = _plain(cfg, t, [2] + ids[1:])
+    assert rel_err(other[1], want[1]) > 0.15                              # the token behind sees which token came first
+    tol = REL[dtype] if dtype == "float32" else 6e-2
+    for sched in ([[("a", len(ids))]], [[("a", 1)]] * len(ids), [[("a", 2)], [("a", 1)], [("a", 3)], [("a", 58)], [("a", 1)], [("a", 6)]]):
+        assert rel_err(run_schedule(eng, {"a": ids}, sched)["a"], want) < tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_sink_takes_the_weight_when_nothing_matches(tmp_path, dtype):
+    """Queries that match no key well (scores far below the sink's): the attention adds next to nothing, where a softmax
+    without the sink would still hand out all its weight.  The first tokens of a sequence (one key, two keys) are such
+    queries.  A sink far below every score changes nothing."""
+    from ithaca_b200 import Engine
+    cfg, t = _needle_parallel("left")
+    t["l0.mix.left.q"] = (-t["l0.mix.left.k"].float()).bfloat16()        # every query points away from every key like it
+    t["l0.mix.left.sink"] = torch.full((1,), 2.0).bfloat16()
+    ids = [1 + (i * i // 3) % 2 for i in range(70)]
+    sched = [[("a", 1)], [("a", 1)], [("a", 2)], [("a", 64)], [("a", 1)], [("a", 1)]]
+    tol = REL[dtype] if dtype == "float32" else 6e-2
+    eng = Engine(_write(tmp_path, cfg, t, "sink"), dtype=dtype, max_tokens=512)
+    want = _plain(cfg, t, ids)
+    assert rel_err(run_schedule(eng, {"a": ids}, sched)["a"], want) < tol
+    t2 = dict(t)
+    t2["l0.mix.left.sink"] = torch.full((1,), -60.0).bfloat16()
+    eng = Engine(_write(tmp_path, cfg, t2, "nosink"), dtype=dtype, max_tokens=512)
+    free = _plain(cfg, t2, ids)
+    assert rel_err(run_schedule(eng, {"a": ids}, sched)["a"], free) < tol
+    assert rel_err(free, want) > 0.15
+
+
+# ------------------------------------------------------------------------------------------ generation
+@pytest.mark.parametrize("graphs", [True, False])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_engine(models, name, graphs):
+    """More prompts than slots, unequal lengths, the generation loop's own batching (and its graph-replayed decode
+    steps, which launch a step ahead and may drop it: the states are kept by parity so that this changes nothing)."""
+    from ithaca_b200 import Engine
+    d, t = models[name]
+    V = CONFIGS[name]["vocab"]
+    prompts = [random_ids(n, V, 60 + n) for n in (1, 6, 70, 20)]
+    eng = Engine(d, dtype="float32", max_tokens=64 * 12, max_slots=3, graphs=graphs)
+    assert (eng._decoder is not None) == graphs                            # every part of the design may be replayed
+    got = eng.generate(prompts, max_tokens=12, temp=0.0, rep_pen=1.0, stop_token_ids=[])
+
+    def check(p, g):
+        lgs = P.forward(CONFIGS[name], t, list(p) + g[:-1])
+        for i, tok in enumerate(g):
+            lg = lgs[len(p) - 1 + i]
+            top2 = torch.topk(lg, 2).values
+            if float(top2[0] - top2[1]) > 1e-4 * float(lg.abs().max()):
+                assert tok == int(lg.argmax()), (len(p), i)
+    for p, g in zip(prompts, got):
+        assert len(g) == 12
+        check(p, g)
+    assert eng.cache.table.n_slots_in_use() == 0
+    got = eng.generate(prompts[:3], max_tokens=9, temp=0.0, rep_pen=1.0, stop_token_ids=[got[0][4], got[2][6]])
+    for p, g in zip(prompts, got):
+        check(p, g)
+
+
+# ------------------------------------------------------------------------------------------ the programs
+def test_trace_replay_and_command_line(models, tmp_path):
+    import subprocess
+    import sys
+    from helpers import ROOT
+    d, t = models["A"]
+    V = 101
+    reqs = {"p": random_ids(70, V, 90), "q": random_ids(3, V, 91), "r": random_ids(130, V, 92)}
+    steps = [{"step": 0, "entries": [{"id": "p", "tokens": reqs["p"][:66], "want": [0, 65]}, {"id": "q", "tokens": reqs["q"][:1], "want": []},
+                                     {"id": "r", "tokens": reqs["r"][:126], "want": [125]}], "end": []}]
+    for i in range(4):
+        ent = [{"id": "p", "tokens": [reqs["p"][66 + i]], "want": [0]}, {"id": "r", "tokens": [reqs["r"][126 + i]], "want": [0]}]
+        if i < 2:
+            ent.insert(1, {"id": "q", "tokens": [reqs["q"][1 + i]], "want": [0] if i == 1 else []})
+        steps.append({"step": 1 + i, "entries": ent, "end": (["q"] if i == 1 else []) + (["p", "r"] if i == 3 else [])})
+    out = tmp_path / "out"
+    for dtype in ("float32", "bfloat16"):
+        p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", str(out),
+                            "--max-tokens", "210"], input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                           timeout=900)
+        assert p.returncode == 0, p.stderr[-3000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(5)]
+        want = {r: _plain(CFG_A, t, ids) for r, ids in reqs.items()}
+        tol = REL[dtype] * (1 if dtype == "float32" else 2)
+        got0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(3, V)
+        assert rel_err(got0, np.stack([want["p"][0], want["p"][65], want["r"][125]])) < tol
+        got2 = np.fromfile(out / "2.f32", dtype="<f4").reshape(3, V)
+        assert rel_err(got2, np.stack([want["p"][67], want["q"][2], want["r"][127]])) < tol
+        got4 = np.fromfile(out / "4.f32", dtype="<f4").reshape(2, V)
+        assert rel_err(got4, np.stack([want["p"][69], want["r"][129]])) < tol
+
+    cli = [sys.executable, os.path.join(ROOT, "bin", "ithaca"), "--model", d, "--dtype", "float32"]
+    p = subprocess.run(cli + ["--describe"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and p.stdout.count("hyper") == 6 and p.stdout.count("gated_delta") == 2 \
+        and p.stdout.count("latent_attention") == 2 and p.stdout.count("read only") == 1 and p.stdout.count("moe") == 2, p.stderr[-2000:]
+    prompt = random_ids(11, V, 93)
+    p = subprocess.run(cli + ["--prompt", ",".join(map(str, prompt)), "-n", "5", "--rep-pen", "1.0", "--stop-ids", ""],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    from ithaca_b200 import Engine
+    eng = Engine(d, dtype="float32", max_tokens=512)
+    assert [int(x) for x in p.stdout.strip().split(",")] == eng.generate([prompt], max_tokens=5, temp=0.0, rep_pen=1.0, stop_token_ids=[])[0]
+
+
+def test_random_weights_written_and_made_on_the_device_agree(tmp_path):
+    """A folder written with random weights (its ranks are then read back from the tensors' shapes) and the same model made
+    on the device give the same logits; the written configuration is read again."""
+    from ithaca_b200 import Engine
+    from ithaca_b200.weights import write_random_model
+    cfg = copy.deepcopy(CFG_A)
+    d = write_random_model(os.path.join(str(tmp_path), "rand"), cfg, seed=5)
+    ids = random_ids(40, 101, 3)
+    a = Engine(d, dtype="float32", max_tokens=256)
+    b = Engine.from_random(cfg, seed=5, dtype="float32", max_tokens=256)
+    la = run_schedule(a, {"a": ids}, [[("a", 40)]])["a"]
+    lb = run_schedule(b, {"a": ids}, [[("a", 40)]])["a"]
+    assert np.array_equal(la, lb) and np.all(np.isfinite(la)) and np.abs(la).max() > 0
