@@ -12,6 +12,11 @@
     python bench.py --only mimadra [--batch B]                  the Mimadra decoder (gated delta rule, latent attention whose second layer
                                                                 reads the first one's rows, windowed attention with a sink) beside a
                                                                 Llama of equal width, heads, feed-forward and depth, in the same form
+    python bench.py --only gunenex [--batch B]                  the Gunenex decoder (several residual streams; delta rule with a decay per key
+                                                                channel; latent attention behind a query latent, a second layer reading the
+                                                                first one's rows; attention with a learned sink beside token-shift time
+                                                                mixing; routed plain experts) beside a Mimadra of equal width, heads,
+                                                                feed-forward and depth (its closest relative here), in the same form
     python bench.py --config 1b-unequal|13b-long                the other two workloads alone, through Engine.generate
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at the given batch with every
@@ -586,6 +591,58 @@ def mimadra_pair(size, vocab=32000):
     return mim, llama, len(kinds)
 
 
+GUNENEX_SIZES = [
+    # name, width, heads, kv heads, head size, feed-forward, latent rank, query latent, streams, time-mixing head size, experts, chosen, layers
+    ("2048 wide, 16 heads of 128, latent of 512, 4 streams", 2048, 16, 4, 128, 8192, 512, 768, 4, 64, 8, 2,
+     ("channel_delta", "latent_attention", "latent_shared", "parallel", "channel_delta")),
+    ("4096 wide, 32 heads of 128, latent of 512, 4 streams", 4096, 32, 8, 128, 14336, 512, 1536, 4, 64, 8, 2,
+     ("channel_delta", "latent_attention", "latent_shared", "parallel")),
+]
+
+
+def gunenex_pair(size, vocab=32000):
+    """The Gunenex configuration of a size and the Mimadra next to it: the same width, heads, head size, latent rank,
+    number of layers and feed-forward width (the routed layers' chosen experts are together as wide as the dense one).
+    Where Gunenex has its parallel layer (attention beside time mixing) Mimadra has its attention; where Gunenex routes
+    (behind the latent layers), Mimadra's feed-forward is dense.  Mimadra's windows are as long as the prompt, so both see
+    every key."""
+    _, d, nh, nkv, hd, ff, rank, q_rank, streams, td, E, top, kinds = size
+    dense = {"kind": "dense", "ff": ff}
+    routed = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": E, "top": top}}
+    g_mixers = {
+        "channel_delta": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "conv": 4, "decay_rank": 64, "gate_rank": 64},
+        "latent_attention": {"heads": nh, "dim": hd, "vdim": hd, "kv_rank": rank, "q_rank": q_rank, "scale": hd ** -0.5},
+        "parallel": {"left": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"base": 500000.0, "dims": hd // 2}},
+                     "right": {"heads": d // td, "dim": td, "rank": 64}},
+    }
+    window = 1 << 20
+    m_mixers = {
+        "channel_delta": ("delta", {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "conv": 4}),
+        "latent_attention": ("latent_attention", {"heads": nh, "dim": hd, "rot_dim": 64, "vdim": hd, "kv_rank": rank, "scale": (hd + 64) ** -0.5,
+                                                  "mask": {"size": window}, "rot": {"base": 500000.0, "dims": 64}}),
+        "parallel": ("attention", {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": window},
+                                   "rot": {"base": 500000.0, "dims": hd // 2}}),
+    }
+    g_layers, m_layers, first_latent = [], [], None
+    for i, k in enumerate(kinds):
+        base = "latent_attention" if k == "latent_shared" else k
+        gm, (mt, mm) = dict(g_mixers[base]), m_mixers[base]
+        mm = dict(mm)
+        if k == "latent_attention" and first_latent is None:
+            first_latent = i
+        if k == "latent_shared":
+            gm["kv_from"] = mm["kv_from"] = first_latent
+        g_layers.append({"type": base, "mixer": gm, "mlp": routed if base == "latent_attention" else dense})
+        m_layers.append({"type": mt, "mixer": mm, "mlp": dense})
+    gun = {"architecture": "Gunenex", "vocab": vocab, "width": d, "streams": streams, "norm": {"eps": 1e-6}, "layers": g_layers}
+    mim = {"architecture": "Mimadra", "vocab": vocab, "width": d, "norm": {"eps": 1e-6}, "logit_softcap": 25.0, "layers": m_layers}
+    return gun, mim, len(kinds)
+
+
+def gunenex_run(pk, batch, steps, warmup, context=2048, prompt=4096):
+    return vebisun_run(pk, batch, steps, warmup, context, prompt, sizes=GUNENEX_SIZES, pair=gunenex_pair, name="gunenex", partner="mimadra")
+
+
 def mimadra_run(pk, batch, steps, warmup, context=2048, prompt=4096):
     return vebisun_run(pk, batch, steps, warmup, context, prompt, sizes=MIMADRA_SIZES, pair=mimadra_pair, name="mimadra")
 
@@ -594,7 +651,7 @@ def tiralix_run(pk, batch, steps, warmup, context=2048, prompt=4096):
     return vebisun_run(pk, batch, steps, warmup, context, prompt, sizes=TIRALIX_SIZES, pair=tiralix_pair, name="tiralix")
 
 
-def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096, sizes=None, pair=None, name="vebisun"):
+def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096, sizes=None, pair=None, name="vebisun", partner="llama"):
     """Per size and model: tok/s of one prompt of ``prompt`` tokens, tok/s of graph-replayed decode steps at ``batch``
     sequences of ``context`` positions, and per kernel of a prompt step and of a decode step its time and its better
     fraction of the two peaks (bytes over the copy bandwidth, operations over the bfloat16 product rate)."""
@@ -606,7 +663,7 @@ def vebisun_run(pk, batch, steps, warmup, context=2048, prompt=4096, sizes=None,
     for size in (sizes or VEBISUN_SIZES):
         veb, llama, runs = (pair or vebisun_pair)(size)
         row = {"size": size[0], "layer_runs": runs, "prompt": prompt, "decode_batch": batch, "decode_context": context}
-        for model, cfg in ((name, veb), ("llama", llama)):
+        for model, cfg in ((name, veb), (partner, llama)):
             vocab = cfg.get("vocab", cfg.get("vocab_size"))
             eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=(batch + 1) * (max(context, prompt) + 128),
                                      ctx=max(context, prompt) + 128, max_step_tokens=max(16384, prompt))
@@ -686,7 +743,7 @@ def main():
                     help="with --only decode / prefill: another context length (decode) or prompt length (prefill) than the default run's")
     ap.add_argument("--config", default=None, choices=["1b-unequal", "13b-long"],
                     help="run one of the other workloads alone and print its figures")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate", "vebisun", "tiralix", "mimadra"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "attention", "products", "marginal", "issue-rate", "vebisun", "tiralix", "mimadra", "gunenex"],
                     help="run one part only and print its figures (for profiling a small case)")
     args = ap.parse_args()
 
@@ -718,6 +775,9 @@ def main():
         return 0
     if args.only == "mimadra":
         print(json.dumps({"only": "mimadra", "peaks": pk, "sizes": mimadra_run(pk, args.batch, min(args.steps, 64), args.warmup)}))
+        return 0
+    if args.only == "gunenex":
+        print(json.dumps({"only": "gunenex", "peaks": pk, "sizes": gunenex_run(pk, args.batch, min(args.steps, 64), args.warmup)}))
         return 0
     if args.only == "issue-rate":
         # what the thread that issues tensor-core products costs: cycles per instruction, one or two issuing threads

@@ -1498,7 +1498,7 @@ DECAY_FORMS = {"softplus": 0, "double_exp": 1}
 def decay_rows(x: torch.Tensor, bias: Optional[torch.Tensor], form: str, A_log: Optional[torch.Tensor] = None,
                per_head: int = 0) -> torch.Tensor:
     """Decays in (0, 1) from projections ``x`` [T, C] (float; a column range may be given).  ``softplus``:
-    exp(-exp(A_log[c // per_head]) * softplus(x + bias)); ``double_exp``: exp(-exp(x + bias)).  Formed in double, rounded once."""
+    exp(-exp(A_log[c // per_head]) * softplus(x + bias)); ``double_exp``: exp(-exp(x + bias)).  Float arithmetic with the accurate exponential and logarithm."""
     _need(x, "x", torch.float32, contiguous=False)
     T, C = x.shape
     if x.stride(1) != 1 or (bias is not None and (bias.numel() != C or bias.dtype != torch.float32)):

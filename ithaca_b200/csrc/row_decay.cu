@@ -14,7 +14,7 @@
 // S = w * S + k v^T.  The state lies as [2, heads, dv, dk] per slot, the two copies by the parity of the position
 // the state belongs to, as for the other recurrences.
 //
-// Around it: the decays themselves (two forms, in double and rounded once), and the token shift (every token's input
+// Around it: the decays themselves (two forms, float with the accurate exponential and logarithm), and the token shift (every token's input
 // mixed with the input one position earlier, which is part of the sequence's state).
 #include "common.cuh"
 
@@ -41,15 +41,15 @@ __global__ void decay_rows_kernel(const float* __restrict__ x, int ldx, const fl
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
         const size_t t = idx / C;
         const int c = (int)(idx - t * C);
-        const double z = (double)x[t * ldx + c] + (bias ? (double)bias[c] : 0.0);
-        double r;
+        const float z = x[t * ldx + c] + (bias ? bias[c] : 0.f);
+        float r;
         if (kind == 0) {
-            const double sp = z > 30.0 ? z : log1p(exp(z));
-            r = exp(-exp((double)A_log[c / per_head]) * sp);
+            const float sp = z > 20.0f ? z : log1pf(expf(z));
+            r = expf(-expf(A_log[c / per_head]) * sp);
         } else {
-            r = exp(-exp(z));
+            r = expf(-expf(z));
         }
-        out[idx] = (float)r;
+        out[idx] = r;
     }
 }
 

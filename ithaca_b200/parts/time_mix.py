@@ -13,9 +13,8 @@ and projected out.
 
 Per sequence and cache entry the mixer keeps S as float32 [2, heads, head_dim, head_dim] (two copies by the parity of the
 position the state belongs to, as the other recurrences do, so that a decode step never overwrites what it read) and the
-input of the last position, float32 [2, hidden] by that position's parity.  The mixes, the four wide products (one launch:
-a batch over r, k, v, g), the decay's two small products with tanh between them, the decays (formed in double, rounded
-once), the recurrence and the output norm: everything behind the products is float32 on both paths; only the products'
+input of the last position, float32 [2, hidden] by that position's parity.  The mixes, the four wide products (one batched
+launch for a few tokens, four launches of the wide-tile product for a prompt), the decay's two small products with tanh between them, the decays, the recurrence and the output norm: everything behind the products is float32 on both paths; only the products'
 operands are 16-bit on the bfloat16 path.
 
 The mixer serves alone or as a branch of a composite (``parts/parallel.py``); as a branch it reads the composite's input
@@ -99,7 +98,14 @@ class ShiftDecayMixer:
         T = x.shape[0]
         mixes = ops.token_shift(x, self.mu, cache.state(SHIFT), ctx)                          # [5, T, d]
         proj = torch.empty((T, 4 * H * D), dtype=torch.float32, device=x.device)             # [r | k | v | g]
-        ops.gemm_heads(mixes[:4].permute(1, 0, 2), self.rkvg, proj.view(T, 4, H * D))
+        if T > 16:
+            # a prompt's portion: each of the four on the product kernel that takes wide token tiles
+            from .linear import gemm
+            for i in range(4):
+                gemm(mixes[i], self.rkvg[i], out=proj[:, i * H * D:(i + 1) * H * D])
+        else:
+            # a few tokens: the four as one batched launch
+            ops.gemm_heads(mixes[:4].permute(1, 0, 2), self.rkvg, proj.view(T, 4, H * D))
         if rt.dtype == "bfloat16":
             from ..csrc import gemm_bf16
             low = gemm_bf16.gemm_act(mixes[4], self.w1.weight, "tanh", rt.act_dtype)          # tanh in the product's epilogue

@@ -167,6 +167,8 @@ def _close(got, want, dtype):
     rows = np.abs(got - want).reshape(-1, want.shape[-1]).max(-1) / max(np.abs(want).max(), 1e-30)
     if dtype == "float32":
         return bool(rows.max() < REL[dtype])
+    if len(rows) < 10:                    # too few rows for a median: each within five times the tolerance (a head's norm
+        return bool(rows.max() < 5 * REL[dtype])          # divides by a first token's small read-out and its rounding with it)
     return bool(np.median(rows) < REL[dtype] and np.quantile(rows, 0.8) < 2.5 * REL[dtype])
 
 
