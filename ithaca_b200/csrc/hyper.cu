@@ -16,7 +16,7 @@
 
 namespace {
 
-constexpr int HY_MAX = 8;            // most streams
+constexpr int HY_MAX = 16;           // most streams (a block of 256 threads brings the 16 x 16 matrix in one go)
 
 __global__ void hyper_start_kernel(const float* __restrict__ x, float* __restrict__ xs, size_t total, int n, int d) {
     ik_pdl_wait();

@@ -264,8 +264,8 @@ class HyperBlock:
     def __init__(self, spec: BlockSpec, tensors: Mapping[str, torch.Tensor], runtime: Runtime):
         has_ff = spec.feed_forward is not None
         self.n = int(spec.params["streams"])
-        if not 1 <= self.n <= 8:
-            raise ValueError(f"hyper block: 1 to 8 streams are supported, found {self.n}")
+        if not 1 <= self.n <= 16:
+            raise ValueError(f"hyper block: 1 to 16 streams are supported, found {self.n}")
         for need in ("mixer",) + (("feed_forward",) if has_ff else ()):
             if need not in spec.norms or need not in spec.params:
                 raise ValueError(f"hyper block: the spec has no '{need}' norm or stream tensors")
