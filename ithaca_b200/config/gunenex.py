@@ -45,8 +45,8 @@ BRANCH_WEIGHT = 0.5        # the parallel mixer is half the sum of its two norme
 TYPES = ("parallel", "latent_attention", "channel_delta")
 # ranks that the file does not give: the first size of a low-rank factor.  A model folder's tensors decide; random
 # weights take these.
-DEFAULT_DECAY_RANK = 16
-DEFAULT_GATE_RANK = 16
+DEFAULT_DECAY_RANK = 32
+DEFAULT_GATE_RANK = 32
 
 
 def _obj(d: Dict[str, Any], key: str, where: str, optional: bool = False) -> Optional[Dict[str, Any]]:

@@ -200,12 +200,14 @@ def dense_feed_forward(h: torch.Tensor, t: Mapping[str, torch.Tensor], p: str) -
 
 
 def routed_feed_forward(h: torch.Tensor, mlp: Mapping, t: Mapping[str, torch.Tensor], p: str,
-                        chosen_out: Optional[List] = None) -> torch.Tensor:
+                        chosen_out: Optional[List] = None, forced: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+    """``forced``: per token the experts to use instead of the ones with the largest scores (for a comparison with 16-bit
+    arithmetic, where two scores a hair apart may change places; the weights are this function's own scores all the same)."""
     top = mlp["router"]["top"]
     s = sigmoid(h @ t[p + ".router"].T)
     out = torch.zeros_like(h)
     for i in range(h.shape[0]):
-        best = sorted(range(s.shape[1]), key=lambda e: (-float(s[i, e]), e))[:top]
+        best = sorted(range(s.shape[1]), key=lambda e: (-float(s[i, e]), e))[:top] if forced is None else list(forced[i])
         if chosen_out is not None:
             chosen_out.append(best)
         for e in best:
@@ -215,8 +217,9 @@ def routed_feed_forward(h: torch.Tensor, mlp: Mapping, t: Mapping[str, torch.Ten
 
 
 def forward(cfg: Mapping, tensors: Mapping[str, torch.Tensor], ids: Sequence[int], dtype=torch.float64,
-            stream_after: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
-    """Logits [T, vocab] of the whole sequence.  ``stream_after`` receives the sum of the streams after every layer."""
+            stream_after: Optional[List[torch.Tensor]] = None, forced: Optional[Mapping[int, Sequence[Sequence[int]]]] = None) -> torch.Tensor:
+    """Logits [T, vocab] of the whole sequence.  ``stream_after`` receives the sum of the streams after every layer.
+    ``forced``: layer -> per token the experts its routed feed-forward is to use."""
     t = {n: w.to(dtype) if w.dtype.is_floating_point else w for n, w in tensors.items()}
     eps = float(cfg["norm"]["eps"])
     n = int(cfg["streams"])
@@ -245,7 +248,7 @@ def forward(cfg: Mapping, tensors: Mapping[str, torch.Tensor], ids: Sequence[int
             if mlp["kind"] == "dense":
                 g = lambda hin: dense_feed_forward(hin, t, p + ".mlp")
             else:
-                g = lambda hin: routed_feed_forward(hin, mlp, t, p + ".mlp")
+                g = lambda hin: routed_feed_forward(hin, mlp, t, p + ".mlp", forced=None if forced is None else forced[i])
             xs = sublayer(xs, p + ".hc2", p + ".norm2", g)
         if stream_after is not None:
             stream_after.append(sum(xs).clone())
