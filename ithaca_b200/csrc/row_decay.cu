@@ -101,7 +101,7 @@ token_shift_ring_kernel(const TX* __restrict__ x, float* __restrict__ ring, cons
 // x1 (q or r) and k come from the float matrix u (row stride ldu) at x1_off / k_off + (query/key head) * dk, v at
 // v_off + h * dv, the decays from dec [T, H * dk], the steps from beta (row stride ldb, one per head; rule 0), the bonus from bonus [H * dk] (rule 1).
 template <int L, int R, int RULE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 row_decay_kernel(const float* __restrict__ u, int ldu, int x1_off, int k_off, int v_off, const float* __restrict__ dec,
                  const float* __restrict__ beta, int ldb, const float* __restrict__ bonus, float* __restrict__ state,
                  const int* __restrict__ slots, const int* __restrict__ cu_seqlens, const int* __restrict__ kv_lens,

@@ -18,7 +18,9 @@ launch for a few tokens, four launches of the wide-tile product for a prompt), t
 operands are 16-bit on the bfloat16 path.
 
 The mixer serves alone or as a branch of a composite (``parts/parallel.py``); as a branch it reads the composite's input
-itself (``reads_input``), since its products take the shifted mixes, not the input.
+itself (``reads_input``), since its products take the shifted mixes, not the input.  It writes its result into a matrix of
+its own (a composite that norms every branch before the sum gives it one); a constant on the result, or a column range of
+a wider matrix as a plain sum of branches would hand it, is refused.
 """
 from __future__ import annotations
 
