@@ -31,10 +31,12 @@ __global__ void hyper_start_kernel(const float* __restrict__ x, float* __restric
     }
 }
 
-template <typename TO>
+// N: the number of streams, fixed at compile time so that the sums over streams are straight-line code.
+template <typename TO, int N>
 __global__ void __launch_bounds__(256)
 hyper_read_kernel(const float* __restrict__ xs, const int* __restrict__ rows_in, const float* __restrict__ a,
-                  const float* __restrict__ w, TO* __restrict__ out, int n, int d, float eps) {
+                  const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+    constexpr int n = N;
     ik_pdl_wait();
     IK_AFTER_WAIT(xs);
     IK_AFTER_WAIT(rows_in);
@@ -43,14 +45,14 @@ hyper_read_kernel(const float* __restrict__ xs, const int* __restrict__ rows_in,
     const int r = blockIdx.x;
     const size_t t = rows_in ? (size_t)rows_in[r] : (size_t)r;
     const float* row = xs + t * n * d;
-    float as[HY_MAX];
+    float as[N];
     #pragma unroll
-    for (int s = 0; s < HY_MAX; s++) as[s] = s < n ? (a ? a[s] : 1.0f) : 0.f;
+    for (int s = 0; s < N; s++) as[s] = a ? a[s] : 1.0f;
     float ss = 0.f;
     for (int i = threadIdx.x; i < d; i += 256) {
         float u = 0.f;
         #pragma unroll
-        for (int s = 0; s < HY_MAX; s++) if (s < n) u = fmaf(as[s], row[(size_t)s * d + i], u);
+        for (int s = 0; s < N; s++) u = fmaf(as[s], row[(size_t)s * d + i], u);
         ss = fmaf(u, u, ss);
     }
     ss = ik_block_sum<256>(ss, red);
@@ -58,15 +60,16 @@ hyper_read_kernel(const float* __restrict__ xs, const int* __restrict__ rows_in,
     for (int i = threadIdx.x; i < d; i += 256) {
         float u = 0.f;
         #pragma unroll
-        for (int s = 0; s < HY_MAX; s++) if (s < n) u = fmaf(as[s], row[(size_t)s * d + i], u);
+        for (int s = 0; s < N; s++) u = fmaf(as[s], row[(size_t)s * d + i], u);
         ik_st(out, (size_t)r * d + i, u * inv * w[i]);
     }
 }
 
-template <typename TO>
+template <typename TO, int N>
 __global__ void __launch_bounds__(256)
 hyper_write_kernel(float* __restrict__ xs, const float* __restrict__ y, const float* __restrict__ M, const float* __restrict__ b,
-                   const float* __restrict__ a_next, const float* __restrict__ w_next, TO* __restrict__ out, int n, int d, float eps) {
+                   const float* __restrict__ a_next, const float* __restrict__ w_next, TO* __restrict__ out, int d, float eps) {
+    constexpr int n = N;
     ik_pdl_wait();
     IK_AFTER_WAIT(xs);
     IK_AFTER_WAIT(y);
@@ -81,21 +84,19 @@ hyper_write_kernel(float* __restrict__ xs, const float* __restrict__ y, const fl
     const float* yr = y + t * d;
     float ss = 0.f;
     for (int i = threadIdx.x; i < d; i += 256) {
-        float old[HY_MAX];
+        float old[N];
         #pragma unroll
-        for (int s = 0; s < HY_MAX; s++) old[s] = s < n ? row[(size_t)s * d + i] : 0.f;
+        for (int s = 0; s < N; s++) old[s] = row[(size_t)s * d + i];
         const float yv = yr[i];
         float u = 0.f;
         #pragma unroll
-        for (int k = 0; k < HY_MAX; k++) {
-            if (k < n) {
-                float v = 0.f;
-                #pragma unroll
-                for (int s = 0; s < HY_MAX; s++) if (s < n) v = fmaf(Ms[s * n + k], old[s], v);
-                v = fmaf(bs[k], yv, v);
-                row[(size_t)k * d + i] = v;
-                u = fmaf(an[k], v, u);
-            }
+        for (int k = 0; k < N; k++) {
+            float v = 0.f;
+            #pragma unroll
+            for (int s = 0; s < N; s++) v = fmaf(Ms[s * n + k], old[s], v);
+            v = fmaf(bs[k], yv, v);
+            row[(size_t)k * d + i] = v;
+            u = fmaf(an[k], v, u);
         }
         ss = fmaf(u, u, ss);
     }
@@ -105,7 +106,7 @@ hyper_write_kernel(float* __restrict__ xs, const float* __restrict__ y, const fl
     for (int i = threadIdx.x; i < d; i += 256) {          // a thread reads back what it wrote itself
         float u = 0.f;
         #pragma unroll
-        for (int k = 0; k < HY_MAX; k++) if (k < n) u = fmaf(an[k], row[(size_t)k * d + i], u);
+        for (int k = 0; k < N; k++) u = fmaf(an[k], row[(size_t)k * d + i], u);
         ik_st(out, t * d + i, u * inv * w_next[i]);
     }
 }
@@ -189,10 +190,20 @@ IK_EXPORT int ik_hyper_read(const float* xs, const int* rows_in, const float* a,
                             int n, int d, float eps, cudaStream_t stream) {
     if (rows < 0 || n <= 0 || n > HY_MAX || d <= 0 || !w) return IK_BAD_ARGUMENT;
     if (rows == 0) return IK_OK;
-    if (out_dtype == IK_F32) IK_RETURN_IF_ERROR(ik_launch(hyper_read_kernel<float>, rows, 256, 0, stream, xs, rows_in, a, w, (float*)out, n, d, eps));
-    else if (out_dtype == IK_BF16)
-        IK_RETURN_IF_ERROR(ik_launch(hyper_read_kernel<__nv_bfloat16>, rows, 256, 0, stream, xs, rows_in, a, w, (__nv_bfloat16*)out, n, d, eps));
-    else return IK_BAD_ARGUMENT;
+    if (out_dtype != IK_F32 && out_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+#define IK_HR(NN)                                                                                                                   \
+    case NN:                                                                                                                        \
+        if (out_dtype == IK_F32)                                                                                                    \
+            IK_RETURN_IF_ERROR(ik_launch(hyper_read_kernel<float, NN>, rows, 256, 0, stream, xs, rows_in, a, w, (float*)out, d, eps)); \
+        else                                                                                                                        \
+            IK_RETURN_IF_ERROR(ik_launch(hyper_read_kernel<__nv_bfloat16, NN>, rows, 256, 0, stream, xs, rows_in, a, w,             \
+                                         (__nv_bfloat16*)out, d, eps));                                                             \
+        break
+    switch (n) {
+        IK_HR(1); IK_HR(2); IK_HR(3); IK_HR(4); IK_HR(5); IK_HR(6); IK_HR(7); IK_HR(8);
+        IK_HR(9); IK_HR(10); IK_HR(11); IK_HR(12); IK_HR(13); IK_HR(14); IK_HR(15); IK_HR(16);
+    }
+#undef IK_HR
     IK_LAUNCH_STATUS();
 }
 
@@ -200,11 +211,20 @@ IK_EXPORT int ik_hyper_write(float* xs, const float* y, const float* M, const fl
                              void* out, int out_dtype, int T, int n, int d, float eps, cudaStream_t stream) {
     if (T < 0 || n <= 0 || n > HY_MAX || d <= 0 || !M || !b || (a_next && (!w_next || !out))) return IK_BAD_ARGUMENT;
     if (T == 0) return IK_OK;
-    if (out_dtype == IK_F32)
-        IK_RETURN_IF_ERROR(ik_launch(hyper_write_kernel<float>, T, 256, 0, stream, xs, y, M, b, a_next, w_next, (float*)out, n, d, eps));
-    else if (out_dtype == IK_BF16)
-        IK_RETURN_IF_ERROR(ik_launch(hyper_write_kernel<__nv_bfloat16>, T, 256, 0, stream, xs, y, M, b, a_next, w_next, (__nv_bfloat16*)out, n, d, eps));
-    else return IK_BAD_ARGUMENT;
+    if (out_dtype != IK_F32 && out_dtype != IK_BF16) return IK_BAD_ARGUMENT;
+#define IK_HW(NN)                                                                                                                   \
+    case NN:                                                                                                                        \
+        if (out_dtype == IK_F32)                                                                                                    \
+            IK_RETURN_IF_ERROR(ik_launch(hyper_write_kernel<float, NN>, T, 256, 0, stream, xs, y, M, b, a_next, w_next, (float*)out, d, eps)); \
+        else                                                                                                                        \
+            IK_RETURN_IF_ERROR(ik_launch(hyper_write_kernel<__nv_bfloat16, NN>, T, 256, 0, stream, xs, y, M, b, a_next, w_next,     \
+                                         (__nv_bfloat16*)out, d, eps));                                                             \
+        break
+    switch (n) {
+        IK_HW(1); IK_HW(2); IK_HW(3); IK_HW(4); IK_HW(5); IK_HW(6); IK_HW(7); IK_HW(8);
+        IK_HW(9); IK_HW(10); IK_HW(11); IK_HW(12); IK_HW(13); IK_HW(14); IK_HW(15); IK_HW(16);
+    }
+#undef IK_HW
     IK_LAUNCH_STATUS();
 }
 
